@@ -1,0 +1,299 @@
+// extern "C" layer of libafb.so: argument validation, variant selection, device context,
+// and the memory / event / stream helpers that mirror the HIP calls of the reference
+// driver (bfAintBGemm.cc:60-66,99-101,148-186; simple_device_mem.hpp:20,25).
+#include <atomic>
+#include <mutex>
+#include <cstring>
+#include "afb_internal.h"
+
+namespace afb {
+
+namespace {
+constexpr int kMaxDevices = 32;
+DeviceCtx g_ctx[kMaxDevices];
+std::mutex g_mutex;
+std::atomic<int> g_last_cuda_error{0};
+std::atomic<unsigned long long> g_launches{0};
+constexpr size_t kSplitKWorkspaceBytes = 32u << 20;
+constexpr size_t kSplitKCounters = 4096;
+}  // namespace
+
+int cuda_fail(cudaError_t e) {
+    g_last_cuda_error.store((int)e);
+    (void)cudaGetLastError();  // clear the sticky-free error state
+    return AFB_ERR_CUDA;
+}
+void count_launch(unsigned n) { g_launches.fetch_add(n); }
+
+DeviceCtx* current_ctx() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    return g_ctx[dev].ready ? &g_ctx[dev] : nullptr;
+}
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+static int validate(const afb_gemm_args* a) {
+    if (!a) return AFB_ERR_BAD_ARG;
+    if (!a->ptr_a || !a->ptr_b || !a->ptr_c || !a->ptr_scale) return AFB_ERR_BAD_ARG;
+    if (a->m == 0 || a->n == 0 || a->k == 0) return AFB_ERR_BAD_ARG;
+    if (a->reserved != 0) return AFB_ERR_BAD_ARG;
+    if (a->b_bits != 8 && a->b_bits != 4) return AFB_ERR_BAD_ARG;
+    if (a->b_encoding > 1 || a->b_layout > 1 || a->scale_dtype > 1 || a->variant > 3) return AFB_ERR_BAD_ARG;
+    if (a->flags & ~AFB_FLAG_C_F32) return AFB_ERR_BAD_ARG;
+    if (a->lda < a->k || a->ldc < a->n) return AFB_ERR_BAD_ARG;
+    if (a->b_layout == AFB_LAYOUT_COL ? a->ldb < a->k : a->ldb < a->n) return AFB_ERR_BAD_ARG;
+    if (a->b_bits == 4 && (a->b_layout != AFB_LAYOUT_COL || (a->k & 1) || (a->ldb & 1))) return AFB_ERR_UNSUPPORTED;
+    if (a->group_size && (a->k % a->group_size)) return AFB_ERR_BAD_ARG;
+    return AFB_OK;
+}
+
+static int resolve(const afb_gemm_args& a, uint32_t* out) {
+    uint32_t v = a.variant;
+    if (a.flags & AFB_FLAG_C_F32) {
+        if (v != AFB_VARIANT_AUTO && v != AFB_VARIANT_NAIVE) return AFB_ERR_UNSUPPORTED;
+        v = AFB_VARIANT_NAIVE;
+    }
+    if (v == AFB_VARIANT_AUTO) {
+        if (a.m <= 16 && decode_supports(a)) v = AFB_VARIANT_DECODE;
+        else if (prefill_supports(a)) v = AFB_VARIANT_PREFILL;
+        else v = AFB_VARIANT_NAIVE;
+    } else if (v == AFB_VARIANT_DECODE) {
+        if (!decode_supports(a)) return AFB_ERR_UNSUPPORTED;
+    } else if (v == AFB_VARIANT_PREFILL) {
+        if (!prefill_supports(a)) return AFB_ERR_UNSUPPORTED;
+    }
+    *out = v;
+    return AFB_OK;
+}
+
+}  // namespace afb
+
+using namespace afb;
+
+#define AFB_CUDA(call)                                  \
+    do {                                                \
+        cudaError_t e__ = (call);                       \
+        if (e__ != cudaSuccess) return cuda_fail(e__);  \
+    } while (0)
+
+extern "C" {
+
+int afb_init(int device) {
+    if (device < 0 || device >= kMaxDevices) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceCtx& c = g_ctx[device];
+    if (c.ready) return AFB_OK;
+    cudaDeviceProp prop;
+    AFB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return AFB_ERR_UNSUPPORTED;  // the kernels are sm_100a only; no fallback
+    c.device = device;
+    c.sm_count = prop.multiProcessorCount;
+    AFB_CUDA(cudaMalloc(&c.status, 4 * sizeof(int32_t)));
+    AFB_CUDA(cudaMemset(c.status, 0, 4 * sizeof(int32_t)));
+    AFB_CUDA(cudaMalloc(&c.splitk_ws, kSplitKWorkspaceBytes));
+    c.splitk_ws_bytes = kSplitKWorkspaceBytes;
+    AFB_CUDA(cudaMalloc(&c.splitk_counters, kSplitKCounters * sizeof(uint32_t)));
+    AFB_CUDA(cudaMemset(c.splitk_counters, 0, kSplitKCounters * sizeof(uint32_t)));
+    c.splitk_counter_count = kSplitKCounters;
+    AFB_CUDA(cudaDeviceSynchronize());
+    c.ready = true;
+    return AFB_OK;
+}
+
+int afb_finalize(void) {
+    int dev = -1;
+    AFB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceCtx& c = g_ctx[dev];
+    if (!c.ready) return AFB_OK;
+    cudaDeviceSynchronize();
+    cudaFree(c.status); cudaFree(c.splitk_ws); cudaFree(c.splitk_counters);
+    for (int i = 0; i < 4; ++i) if (c.stage[i]) cudaFree(c.stage[i]);
+    c = DeviceCtx();
+    return AFB_OK;
+}
+
+int afb_device_count(int* count) {
+    if (!count) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaGetDeviceCount(count));
+    return AFB_OK;
+}
+int afb_sm_count(int* count) {
+    DeviceCtx* c = current_ctx();
+    if (!c) return AFB_ERR_NOT_INIT;
+    if (!count) return AFB_ERR_BAD_ARG;
+    *count = c->sm_count;
+    return AFB_OK;
+}
+
+int afb_malloc(void** ptr, size_t bytes) {
+    if (!ptr) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaMalloc(ptr, bytes ? bytes : 1));
+    return AFB_OK;
+}
+int afb_free(void* ptr) { AFB_CUDA(cudaFree(ptr)); return AFB_OK; }
+int afb_malloc_host(void** ptr, size_t bytes) {
+    if (!ptr) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaMallocHost(ptr, bytes ? bytes : 1));
+    return AFB_OK;
+}
+int afb_free_host(void* ptr) { AFB_CUDA(cudaFreeHost(ptr)); return AFB_OK; }
+int afb_memcpy_h2d(void* dst, const void* src, size_t bytes) { AFB_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice)); return AFB_OK; }
+int afb_memcpy_d2h(void* dst, const void* src, size_t bytes) { AFB_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost)); return AFB_OK; }
+int afb_memcpy_d2d(void* dst, const void* src, size_t bytes) { AFB_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice)); return AFB_OK; }
+int afb_memset(void* dst, int value, size_t bytes) { AFB_CUDA(cudaMemset(dst, value, bytes)); return AFB_OK; }
+
+int afb_event_create(void** event) {
+    if (!event) return AFB_ERR_BAD_ARG;
+    cudaEvent_t e;
+    AFB_CUDA(cudaEventCreate(&e));
+    *event = e;
+    return AFB_OK;
+}
+int afb_event_record(void* event, void* stream) { AFB_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream)); return AFB_OK; }
+int afb_event_sync(void* event) { AFB_CUDA(cudaEventSynchronize((cudaEvent_t)event)); return AFB_OK; }
+int afb_event_elapsed_ms(float* ms, void* start, void* stop) {
+    if (!ms) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return AFB_OK;
+}
+int afb_event_destroy(void* event) { AFB_CUDA(cudaEventDestroy((cudaEvent_t)event)); return AFB_OK; }
+int afb_stream_create(void** stream) {
+    if (!stream) return AFB_ERR_BAD_ARG;
+    cudaStream_t s;
+    AFB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = s;
+    return AFB_OK;
+}
+int afb_stream_sync(void* stream) { AFB_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); return AFB_OK; }
+int afb_stream_destroy(void* stream) { AFB_CUDA(cudaStreamDestroy((cudaStream_t)stream)); return AFB_OK; }
+int afb_device_sync(void) { AFB_CUDA(cudaDeviceSynchronize()); return AFB_OK; }
+
+int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant) {
+    if (!variant) return AFB_ERR_BAD_ARG;
+    int rc = validate(args);
+    if (rc) return rc;
+    return resolve(*args, variant);
+}
+
+int afb_gemm_launch(const afb_gemm_args* args, void* stream) {
+    int rc = validate(args);
+    if (rc) return rc;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    uint32_t v;
+    rc = resolve(*args, &v);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (v) {
+        case AFB_VARIANT_DECODE:  return launch_decode(*args, ctx, s);
+        case AFB_VARIANT_PREFILL: return launch_prefill(*args, ctx, s);
+        default:                  return launch_naive(*args, ctx, s);
+    }
+}
+
+static size_t b_bytes(const afb_gemm_args& a) {
+    const size_t ld_bytes = (size_t)a.ldb * a.b_bits / 8;
+    const size_t rows = a.b_layout == AFB_LAYOUT_COL ? a.n : a.k;
+    const size_t cols_bytes = (size_t)(a.b_layout == AFB_LAYOUT_COL ? a.k : a.n) * a.b_bits / 8;
+    return (rows - 1) * ld_bytes + cols_bytes;  // the size rule of bfAintBGemm.cc:68-76
+}
+
+int afb_gemm_host(const afb_gemm_args* h, void* stream) {
+    int rc = validate(h);
+    if (rc) return rc;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    const size_t c_elt = (h->flags & AFB_FLAG_C_F32) ? 4 : 2;
+    const size_t scale_elt = h->scale_dtype == AFB_SCALE_BF16 ? 2 : 4;
+    const size_t scale_cnt = h->group_size ? (size_t)h->n * (h->k / h->group_size) : h->n;
+    const size_t need[4] = {((size_t)(h->m - 1) * h->ldc + h->n) * c_elt, ((size_t)(h->m - 1) * h->lda + h->k) * 2,
+                            b_bytes(*h), scale_cnt * scale_elt};
+    for (int i = 0; i < 4; ++i) {
+        if (ctx->stage_bytes[i] < need[i]) {
+            if (ctx->stage[i]) AFB_CUDA(cudaFree(ctx->stage[i]));
+            ctx->stage[i] = nullptr; ctx->stage_bytes[i] = 0;
+            AFB_CUDA(cudaMalloc(&ctx->stage[i], need[i]));
+            ctx->stage_bytes[i] = need[i];
+        }
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, s));
+    AFB_CUDA(cudaMemcpyAsync(ctx->stage[2], h->ptr_b, need[2], cudaMemcpyHostToDevice, s));
+    AFB_CUDA(cudaMemcpyAsync(ctx->stage[3], h->ptr_scale, need[3], cudaMemcpyHostToDevice, s));
+    afb_gemm_args d = *h;
+    d.ptr_c = ctx->stage[0]; d.ptr_a = ctx->stage[1]; d.ptr_b = ctx->stage[2]; d.ptr_scale = ctx->stage[3];
+    rc = afb_gemm_launch(&d, stream);
+    if (rc) return rc;
+    AFB_CUDA(cudaMemcpyAsync(h->ptr_c, ctx->stage[0], need[0], cudaMemcpyDeviceToHost, s));
+    AFB_CUDA(cudaStreamSynchronize(s));
+    return AFB_OK;
+}
+
+int afb_dequant_dump(const afb_gemm_args* args, void* out_bf16, void* stream) {
+    if (!args || !args->ptr_b || !out_bf16 || args->n == 0 || args->k == 0) return AFB_ERR_BAD_ARG;
+    if (args->b_bits != 8 && args->b_bits != 4) return AFB_ERR_BAD_ARG;
+    if (args->group_size && !args->ptr_scale) return AFB_ERR_BAD_ARG;
+    if (args->b_bits == 4 && args->b_layout != AFB_LAYOUT_COL) return AFB_ERR_UNSUPPORTED;
+    if (!current_ctx()) return AFB_ERR_NOT_INIT;
+    return launch_dequant_dump(*args, out_bf16, (cudaStream_t)stream);
+}
+
+int afb_read_status(int32_t out[4]) {
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    if (!out) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaDeviceSynchronize());
+    AFB_CUDA(cudaMemcpy(out, ctx->status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    AFB_CUDA(cudaMemset(ctx->status, 0, 4 * sizeof(int32_t)));
+    return AFB_OK;
+}
+
+int afb_ipc_export(void* dev_ptr, unsigned char handle[AFB_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == AFB_IPC_HANDLE_BYTES, "handle size");
+    if (!dev_ptr || !handle) return AFB_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    AFB_CUDA(cudaIpcGetMemHandle(&h, dev_ptr));
+    memcpy(handle, &h, sizeof(h));
+    return AFB_OK;
+}
+int afb_ipc_import(const unsigned char handle[AFB_IPC_HANDLE_BYTES], void** dev_ptr) {
+    if (!dev_ptr || !handle) return AFB_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    AFB_CUDA(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return AFB_OK;
+}
+int afb_ipc_release(void* dev_ptr) { AFB_CUDA(cudaIpcCloseMemHandle(dev_ptr)); return AFB_OK; }
+
+const char* afb_status_string(int status) {
+    switch (status) {
+        case AFB_OK: return "ok";
+        case AFB_ERR_BAD_ARG: return "bad argument";
+        case AFB_ERR_UNSUPPORTED: return "unsupported shape, layout or mode for the requested variant";
+        case AFB_ERR_CUDA: return "CUDA call failed";
+        case AFB_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case AFB_ERR_NOT_INIT: return "afb_init was not called on the current device";
+        case AFB_ERR_TOO_LARGE: return "request exceeds a fixed capacity";
+        default: return "unknown status";
+    }
+}
+int afb_last_cuda_error(void) { return g_last_cuda_error.load(); }
+const char* afb_last_cuda_error_string(void) { return cudaGetErrorString((cudaError_t)g_last_cuda_error.load()); }
+unsigned long long afb_launch_count(void) { return g_launches.load(); }
+const char* afb_version(void) { return "afb 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+// In-register unpack of packed int8 / int4 weights to exact bf16 pairs.
+//
+// The reference kernel splices each byte into the mantissa of 2^23 and subtracts
+// 2^23 + 128 in fp32 (bf16gemm_kernel_gfx90a.s:18-27, constants :204-210).  bf16 has an
+// 8-bit significand, so on sm_100a the same idea is done directly in packed bf16:
+//   int8:  v = (v & 0x7f) - 128 * bit7.   0x4300 | (v & 0x7f) is the bf16 128 + (v & 0x7f)
+//          and 0xC300 | (v & 0x80) is the bf16 -128 (bit7 = 0) or -256 (bit7 = 1); their
+//          bf16 sum is the exact integer v.  Two weights per 32-bit lane operation.
+//   int4:  0x4300 | (q ^ 8) is the bf16 128 + (q + 8); subtracting 136 gives q exactly.
+// All results are integers of magnitude <= 128, exactly representable in bf16.
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace afb {
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// (a & b) | c
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// (a & b) ^ c
+__device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// x holds two two's-complement int8 values in bits [0,8) and [16,24) (other bits ignored).
+// Returns the two exact bf16 values, low half = the value from bits [0,8).
+__device__ __forceinline__ uint32_t s8pair_to_bf16x2(uint32_t x) {
+    const uint32_t lo = lop3_and_or(x, 0x007f007fu, 0x43004300u);  // 128 + (v & 0x7f)
+    const uint32_t hi = lop3_and_or(x, 0x00800080u, 0xC300C300u);  // -128 - 128 * bit7
+    return bf16x2_add(lo, hi);
+}
+
+// Four consecutive int8 (two's complement) of word w -> {k0,k1} and {k2,k3} as bf16x2.
+__device__ __forceinline__ void s8x4_to_bf16_natural(uint32_t w, uint32_t& p01, uint32_t& p23) {
+    p01 = s8pair_to_bf16x2(prmt(w, 0u, 0x4140u));
+    p23 = s8pair_to_bf16x2(prmt(w, 0u, 0x4342u));
+}
+// Same bytes, cheaper pairing: {k0,k2} and {k1,k3} (the consumer permutes its other operand).
+__device__ __forceinline__ void s8x4_to_bf16_strided(uint32_t w, uint32_t& p02, uint32_t& p13) {
+    p02 = s8pair_to_bf16x2(w);
+    p13 = s8pair_to_bf16x2(w >> 8);
+}
+
+// magic = 0x43084308 for two's-complement nibbles, 0x43004300 for offset-binary (+8) nibbles.
+// x holds two nibbles in bits [0,4) and [16,20) (other bits ignored) -> two exact bf16.
+__device__ __forceinline__ uint32_t s4pair_to_bf16x2(uint32_t x, uint32_t magic) {
+    return bf16x2_sub(lop3_and_xor(x, 0x000f000fu, magic), 0x43084308u);  // - 136
+}
+// Eight consecutive nibbles of w (k0 in bits [0,4)) -> {k0,k1},{k2,k3},{k4,k5},{k6,k7}.
+__device__ __forceinline__ void s4x8_to_bf16_natural(uint32_t w, uint32_t magic, uint32_t p[4]) {
+    const uint32_t sh = w >> 4;
+    p[0] = s4pair_to_bf16x2(prmt(w, sh, 0x0400u), magic);
+    p[1] = s4pair_to_bf16x2(prmt(w, sh, 0x0501u), magic);
+    p[2] = s4pair_to_bf16x2(prmt(w, sh, 0x0602u), magic);
+    p[3] = s4pair_to_bf16x2(prmt(w, sh, 0x0703u), magic);
+}
+// Cheaper pairing: {k0,k4},{k1,k5},{k2,k6},{k3,k7}.
+__device__ __forceinline__ void s4x8_to_bf16_strided(uint32_t w, uint32_t magic, uint32_t p[4]) {
+    p[0] = s4pair_to_bf16x2(w, magic);
+    p[1] = s4pair_to_bf16x2(w >> 4, magic);
+    p[2] = s4pair_to_bf16x2(w >> 8, magic);
+    p[3] = s4pair_to_bf16x2(w >> 12, magic);
+}
+
+__device__ __forceinline__ uint32_t bf16_dup(uint16_t s) { return (uint32_t)s * 0x00010001u; }
+
+}  // namespace afb

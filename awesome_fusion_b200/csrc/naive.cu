@@ -1,0 +1,148 @@
+// Naive variant: one thread per C element, fp32, the loop of the reference's CPU check
+// (host_ref.hpp:15-24: acc += a * (b * scale), k ascending, no fused multiply-add), for
+// every layout / bit-width / encoding / scale mode the argument block can express.
+// It is the GPU-side cross-check for the fast variants at sizes the CPU cannot finish,
+// and the variant AFB_VARIANT_AUTO falls back to for B in the reference's [K,N] layout.
+//
+// Also here: the dequant-dump kernel, which writes the weights exactly as the fast
+// kernels hand them to the tensor cores (it calls the same device functions).
+#include "afb_internal.h"
+#include "dequant.cuh"
+
+namespace afb {
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+
+// Scalar decode of weight (n, k) -> integer value as float.
+__device__ __forceinline__ float load_q(const uint8_t* __restrict__ b, uint32_t n, uint32_t k, uint32_t ldb,
+                                        uint32_t bits, uint32_t enc, uint32_t layout) {
+    if (bits == 8) {
+        const size_t idx = layout == AFB_LAYOUT_COL ? (size_t)n * ldb + k : (size_t)k * ldb + n;
+        const uint8_t u = b[idx];
+        const int v = enc == AFB_ENC_OFFSET_BINARY ? (int)u - 128 : (int)(int8_t)u;
+        return (float)v;
+    }
+    // 4-bit, [N,K] only: two per byte along K, low nibble = even k
+    const size_t byte = (size_t)n * (ldb >> 1) + (k >> 1);
+    const uint32_t nib = (b[byte] >> ((k & 1u) * 4u)) & 0xFu;
+    const int v = enc == AFB_ENC_OFFSET_BINARY ? (int)nib - 8 : (int)((nib ^ 8u)) - 8;
+    return (float)v;
+}
+
+__device__ __forceinline__ float load_scale(const void* __restrict__ s, size_t idx, uint32_t dtype) {
+    return dtype == AFB_SCALE_BF16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(s)[idx])
+                                   : reinterpret_cast<const float*>(s)[idx];
+}
+
+__global__ void __launch_bounds__(256) naive_gemm_kernel(afb_gemm_args a) {
+    const uint32_t n = blockIdx.x * 32 + (threadIdx.x & 31);
+    const uint32_t m = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (m >= a.m || n >= a.n) return;
+    const uint16_t* __restrict__ pa = reinterpret_cast<const uint16_t*>(a.ptr_a) + (size_t)m * a.lda;
+    const uint8_t* __restrict__ pb = reinterpret_cast<const uint8_t*>(a.ptr_b);
+    const uint32_t groups = a.group_size ? a.k / a.group_size : 0;
+    float scale = a.group_size ? 0.f : load_scale(a.ptr_scale, n, a.scale_dtype);
+    float acc = 0.f;
+    for (uint32_t k = 0; k < a.k; ++k) {
+        if (a.group_size && (k % a.group_size) == 0)
+            scale = load_scale(a.ptr_scale, (size_t)n * groups + k / a.group_size, a.scale_dtype);
+        const float q = load_q(pb, n, k, a.ldb, a.b_bits, a.b_encoding, a.b_layout);
+        const float w = __fmul_rn(q, scale);
+        acc = __fadd_rn(acc, __fmul_rn(bf16_bits_to_f32(pa[k]), w));
+    }
+    if (a.flags & AFB_FLAG_C_F32)
+        reinterpret_cast<float*>(a.ptr_c)[(size_t)m * a.ldc + n] = acc;
+    else
+        reinterpret_cast<__nv_bfloat16*>(a.ptr_c)[(size_t)m * a.ldc + n] = __float2bfloat16_rn(acc);
+}
+
+int launch_naive(const afb_gemm_args& a, DeviceCtx*, cudaStream_t s) {
+    dim3 grid((a.n + 31) / 32, (a.m + 7) / 8);
+    if (grid.y > 65535) return AFB_ERR_UNSUPPORTED;
+    naive_gemm_kernel<<<grid, 256, 0, s>>>(a);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
+// ---------------------------------------------------------------------------------
+// Dequant dump: each thread converts one 16-byte piece of B with the fast-path
+// routines and stores the bf16 result in B's own logical layout.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint16_t* __restrict__ out) {
+    const uint8_t* __restrict__ pb = reinterpret_cast<const uint8_t*>(a.ptr_b);
+    const uint32_t xormask = a.b_encoding == AFB_ENC_OFFSET_BINARY ? 0x80808080u : 0u;
+    const uint32_t magic4 = a.b_encoding == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
+    if (a.b_layout == AFB_LAYOUT_COL) {
+        const uint32_t per16 = a.b_bits == 8 ? 16u : 32u;  // weights per 16-byte piece
+        const uint32_t pieces_per_row = a.k / per16;
+        const size_t total = (size_t)a.n * pieces_per_row;
+        const uint32_t groups = a.group_size ? a.k / a.group_size : 0;
+        for (size_t id = blockIdx.x * (size_t)blockDim.x + threadIdx.x; id < total; id += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t n = (uint32_t)(id / pieces_per_row);
+            const uint32_t k0 = (uint32_t)(id % pieces_per_row) * per16;
+            const size_t row_bytes = a.b_bits == 8 ? (size_t)a.ldb : (size_t)(a.ldb >> 1);
+            const uint4 raw = *reinterpret_cast<const uint4*>(pb + (size_t)n * row_bytes + (a.b_bits == 8 ? k0 : (k0 >> 1)));
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            uint32_t sc = 0;
+            if (a.group_size) {
+                // a 16-byte piece never straddles a group (group_size is a multiple of 32)
+                const size_t si = (size_t)n * groups + k0 / a.group_size;
+                uint16_t sb;
+                if (a.scale_dtype == AFB_SCALE_BF16) sb = reinterpret_cast<const uint16_t*>(a.ptr_scale)[si];
+                else sb = __bfloat16_as_ushort(__float2bfloat16_rn(reinterpret_cast<const float*>(a.ptr_scale)[si]));
+                sc = bf16_dup(sb);
+            }
+            uint32_t* o = reinterpret_cast<uint32_t*>(out + (size_t)n * a.k + k0);
+            if (a.b_bits == 8) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t p01, p23;
+                    s8x4_to_bf16_natural(w[j] ^ xormask, p01, p23);
+                    if (a.group_size) { p01 = bf16x2_mul(p01, sc); p23 = bf16x2_mul(p23, sc); }
+                    o[2 * j] = p01; o[2 * j + 1] = p23;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t p[4];
+                    s4x8_to_bf16_natural(w[j], magic4, p);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[4 * j + i] = a.group_size ? bf16x2_mul(p[i], sc) : p[i];
+                }
+            }
+        }
+    } else {
+        // [K,N] int8: 4 consecutive n per thread, scalar stores (this layout has no fast GEMM variant;
+        // the strided-pair routine is exercised here so that it is covered bit-exactly too)
+        const uint32_t n4 = a.n / 4;
+        const size_t total = (size_t)a.k * n4;
+        for (size_t id = blockIdx.x * (size_t)blockDim.x + threadIdx.x; id < total; id += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t k = (uint32_t)(id / n4);
+            const uint32_t n0 = (uint32_t)(id % n4) * 4;
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(pb + (size_t)k * a.ldb + n0) ^ xormask;
+            uint32_t p02, p13;
+            s8x4_to_bf16_strided(w, p02, p13);
+            uint16_t v[4] = {(uint16_t)(p02 & 0xffff), (uint16_t)(p13 & 0xffff), (uint16_t)(p02 >> 16), (uint16_t)(p13 >> 16)};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[(size_t)k * a.n + n0 + i] = v[i];
+        }
+    }
+}
+
+int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s) {
+    if (a.b_layout == AFB_LAYOUT_COL) {
+        const uint32_t per16 = a.b_bits == 8 ? 16u : 32u;
+        if (a.k % per16 || (a.b_bits == 8 ? a.ldb % 16 : a.ldb % 32)) return AFB_ERR_UNSUPPORTED;
+        if (a.group_size && a.group_size % 32) return AFB_ERR_UNSUPPORTED;
+    } else {
+        if (a.b_bits != 8 || a.n % 4 || a.ldb % 4 || a.group_size) return AFB_ERR_UNSUPPORTED;
+    }
+    if ((uintptr_t)a.ptr_b % 16) return AFB_ERR_BAD_ARG;
+    dequant_dump_kernel<<<296, 256, 0, s>>>(a, reinterpret_cast<uint16_t*>(out));
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
+}  // namespace afb

@@ -1,0 +1,144 @@
+/*
+ * afb_capi.h — C ABI of the B200 (sm_100a) bfAintBGemm library (libafb.so).
+ *
+ * The reference host driver (bfAintBGemm/bfAintBGemm.cc) reaches its GPU through the
+ * HIP runtime and a hand-loaded code object.  Every HIP entry point that driver uses
+ * has exactly one counterpart here, so a host program written against the reference's
+ * headers can be re-targeted by swapping the calls one for one.  All functions take
+ * plain pointers and sizes, return an int status (0 = AFB_OK, negative = AFB_ERR_*)
+ * and never abort or trap.  No CUDA or torch type appears in a signature: streams and
+ * events are opaque void*.
+ *
+ * The computation:  C[M,N] (bf16) = A[M,K] (bf16) x dequant(B)^T, fp32 accumulation,
+ * where B holds 8-bit or 4-bit integers and dequant multiplies by a per-output-channel
+ * scale[N] or a per-group scale[N][K/group].
+ */
+#ifndef AFB_CAPI_H_
+#define AFB_CAPI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------- */
+#define AFB_OK               0
+#define AFB_ERR_BAD_ARG     (-1)  /* null pointer, zero dimension, misaligned pointer/ld */
+#define AFB_ERR_UNSUPPORTED (-2)  /* legal request that no kernel variant covers       */
+#define AFB_ERR_CUDA        (-3)  /* a CUDA runtime/driver call failed; see afb_last_cuda_error */
+#define AFB_ERR_TIMEOUT     (-4)  /* a bounded device-side wait gave up                 */
+#define AFB_ERR_NOT_INIT    (-5)  /* afb_init was not called for the current device     */
+#define AFB_ERR_TOO_LARGE   (-6)  /* request exceeds a fixed capacity (e.g. static scratch) */
+
+/* ---- enumerations carried in afb_gemm_args ------------------------------------ */
+#define AFB_ENC_TWOS_COMPLEMENT 0u /* int8 in [-128,127]; int4 in [-8,7]                */
+#define AFB_ENC_OFFSET_BINARY   1u /* byte = value + 128 (reference: mem_transfer.hpp:30); nibble = value + 8 */
+
+#define AFB_LAYOUT_ROW 0u /* B is [K,N], N contiguous — the reference's "rrr" (bfAintBGemm.cc:20-23,51) */
+#define AFB_LAYOUT_COL 1u /* B is [N,K], K contiguous — ColumnMajor tag of gemm_tensor_layout.hpp:16-19 */
+
+#define AFB_SCALE_F32  0u
+#define AFB_SCALE_BF16 1u
+
+#define AFB_VARIANT_AUTO    0u /* decode for M <= 16, prefill above, naive where neither applies */
+#define AFB_VARIANT_DECODE  1u /* memory-bound small-M kernel                                   */
+#define AFB_VARIANT_PREFILL 2u /* TMA + tcgen05/TMEM kernel                                    */
+#define AFB_VARIANT_NAIVE   3u /* one thread per output element, fp32, order of host_ref.hpp:15-24 */
+
+#define AFB_FLAG_C_F32 1u /* naive variant only: C is fp32 [M,N] instead of bf16 (exact comparison with the CPU oracle) */
+
+/*
+ * Kernel argument block.  The first ten fields are the reference's packed kernarg
+ * block, same order and types (bfAintBGemm.cc:119-133; bf16gemm_kernel_gfx90a.s:97-108).
+ * Leading dimensions are in ELEMENTS (for 4-bit B: in 4-bit elements, so bytes = ldb/2).
+ * The appended fields select what the reference fixed at compile time.
+ */
+typedef struct afb_gemm_args {
+    void*    ptr_c;      /* bf16 [M,N] row-major, ldc                                   */
+    void*    ptr_a;      /* bf16 [M,K] row-major, lda                                   */
+    void*    ptr_b;      /* packed integers, see b_layout / b_bits / b_encoding         */
+    void*    ptr_scale;  /* group_size == 0: [N];  else [N][K/group_size] (n-major)      */
+    uint32_t m, n, k;
+    uint32_t lda, ldb, ldc;
+    uint32_t b_bits;      /* 8 or 4 (4: two per byte along K, low nibble = even k; COL layout only) */
+    uint32_t b_encoding;  /* AFB_ENC_*                                                   */
+    uint32_t b_layout;    /* AFB_LAYOUT_*                                                */
+    uint32_t scale_dtype; /* AFB_SCALE_*                                                 */
+    uint32_t group_size;  /* 0 = one scale per output channel; else K-elements per scale */
+    uint32_t variant;     /* AFB_VARIANT_*                                               */
+    uint32_t flags;       /* AFB_FLAG_*                                                  */
+    uint32_t reserved;    /* must be 0                                                   */
+} afb_gemm_args;
+
+/* ---- device / memory / events: one per HIP call of the reference driver --------- */
+/* hipSetDevice (bfAintBGemm.cc:63) + module load (:65-66): selects the device, creates
+ * the per-device context (status word, split-K workspace, tensor-map entry point).   */
+int afb_init(int device);
+int afb_finalize(void);
+int afb_device_count(int* count);
+int afb_sm_count(int* count);
+/* hipMalloc / hipFree (simple_device_mem.hpp:20,25) */
+int afb_malloc(void** ptr, size_t bytes);
+int afb_free(void* ptr);
+/* pinned host memory for the end-to-end path (no reference counterpart: the reference uses malloc) */
+int afb_malloc_host(void** ptr, size_t bytes);
+int afb_free_host(void* ptr);
+/* hipMemcpy H2D / D2H (bfAintBGemm.cc:99-101,158,211) */
+int afb_memcpy_h2d(void* dst, const void* src, size_t bytes);
+int afb_memcpy_d2h(void* dst, const void* src, size_t bytes);
+int afb_memcpy_d2d(void* dst, const void* src, size_t bytes);
+int afb_memset(void* dst, int value, size_t bytes);
+/* hipEventCreate / Record / Synchronize / ElapsedTime / Destroy (bfAintBGemm.cc:171-184) */
+int afb_event_create(void** event);
+int afb_event_record(void* event, void* stream);
+int afb_event_sync(void* event);
+int afb_event_elapsed_ms(float* ms, void* start, void* stop);
+int afb_event_destroy(void* event);
+int afb_stream_create(void** stream);
+int afb_stream_sync(void* stream);
+int afb_stream_destroy(void* stream);
+/* hipDeviceSynchronize (bfAintBGemm.cc:173,181) */
+int afb_device_sync(void);
+
+/* ---- the hot path ------------------------------------------------------------- */
+/* hipModuleLaunchKernel (bfAintBGemm.cc:152,176): validates args, picks the variant,
+ * decides grid/block/shared memory/tensor maps itself and launches asynchronously on
+ * `stream` (NULL = the default stream).  Pointers are DEVICE pointers.               */
+int afb_gemm_launch(const afb_gemm_args* args, void* stream);
+/* Which variant AFB_VARIANT_AUTO resolves to for these args (no launch). */
+int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
+/* The whole reference sequence "H2D x3, launch, D2H" (bfAintBGemm.cc:99-101,152,211)
+ * as one call on HOST pointers: copies A, B, scale to library-owned device staging,
+ * launches, copies C back, and returns when C is in host memory.                     */
+int afb_gemm_host(const afb_gemm_args* host_args, void* stream);
+/* Dequantised weights exactly as the kernels feed them to the tensor cores:
+ * out is bf16 with B's logical shape and layout ([N,K] ld=K for COL, [K,N] ld=N for ROW).
+ * group_size == 0: the exact integer value; else bf16_rn(float(q) * float(scale)).
+ * This is the bit-exact unpack + dequant contract (reference: .dequant_int8_4x1,
+ * bf16gemm_kernel_gfx90a.s:18-55, constants :204-210).                                */
+int afb_dequant_dump(const afb_gemm_args* args, void* out_bf16, void* stream);
+/* Reads (synchronously) the status words the last kernels on this device wrote:
+ * out[0] = 0 or AFB_ERR_TIMEOUT, out[1..3] = where the wait gave up.  Clears them.   */
+int afb_read_status(int32_t out[4]);
+
+/* ---- row-parallel (K-split) exchange over peer memory --------------------------- */
+/* No reference counterpart (the reference is single-GPU, bfAintBGemm.cc:63).          */
+#define AFB_IPC_HANDLE_BYTES 64
+int afb_ipc_export(void* dev_ptr, unsigned char handle[AFB_IPC_HANDLE_BYTES]);
+int afb_ipc_import(const unsigned char handle[AFB_IPC_HANDLE_BYTES], void** dev_ptr);
+int afb_ipc_release(void* dev_ptr);
+
+/* ---- diagnostics ------------------------------------------------------------- */
+const char* afb_status_string(int status);
+int afb_last_cuda_error(void);             /* cudaError_t of the last failing CUDA call */
+const char* afb_last_cuda_error_string(void);
+/* Number of kernels this library launched since afb_init (all variants). */
+unsigned long long afb_launch_count(void);
+const char* afb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AFB_CAPI_H_ */

@@ -1,0 +1,71 @@
+"""GPU tests at the full benchmark sizes, where the CPU oracle would take hours: size-independent
+properties plus oracle-checked samples.
+  * sampled activation rows checked against the CPU oracle (each entry is a full K-long dot product);
+  * fast variants against the naive variant (itself bit-exact with the oracle, test_gpu_parity.py) on a row subset;
+  * linearity: doubling every scale doubles C exactly (a power of two commutes with every rounding);
+  * column sharding: the N-split halves concatenate to the unsplit result bit for bit."""
+import numpy as np
+import pytest
+
+import afb_testlib as T
+import awesome_fusion_b200 as pkg
+from test_gpu_parity import check_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_rows(afb, case, rows, variant):
+    sub = T.Case(**{**case.__dict__, "m": len(rows), "a": np.ascontiguousarray(case.a[rows])})
+    out, _ = T.run_case(afb, sub, variant=variant)
+    return out
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_decode_config_full(afb, oracle, m):
+    case = T.make_case(m, 4096, 4096, seed=0)
+    got, _ = T.run_case(afb, case)
+    check_close(oracle, oracle.gemm(case, threads=8), got, f"decode 4096x4096 M={m}")
+
+
+def test_prefill_config_full(afb, oracle):
+    case = T.make_case(2048, 11008, 4096, seed=0)
+    dc = T.DeviceCase(afb, case)
+    try:
+        assert afb.resolve_variant(dc.args()) == pkg.VARIANT_PREFILL
+        afb.gemm_launch(dc.args()); afb.device_sync()
+        got, _ = dc.result()
+        assert afb.read_status()[0] == 0
+        rows = [0, 1, 127, 128, 1000, 2047]
+        ref = oracle.gemm(case, threads=8, rows=rows)
+        check_close(oracle, ref, got[rows], "prefill 2048x11008x4096 sampled rows")
+        # against the naive variant on 64 rows
+        rows64 = list(range(960, 1024))
+        check_close(oracle, T.np_bf16_to_f32(_run_rows(afb, case, rows64, pkg.VARIANT_NAIVE)), got[rows64], "prefill vs naive", tol=8e-3)
+        # linearity in the scales (x2 is exact in fp32 and bf16)
+        afb.h2d(dc.d_s, (case.scale * 2).astype(np.float32))
+        afb.gemm_launch(dc.args()); afb.device_sync()
+        got2, _ = dc.result()
+        assert np.array_equal(T.np_bf16_to_f32(got2), 2 * T.np_bf16_to_f32(got))
+    finally:
+        dc.close()
+
+
+@pytest.mark.parametrize("m", [1, 16, 128])
+def test_int4_group_config(afb, oracle, m):
+    case = T.make_case(m, 28672, 8192, bits=4, group=128, seed=0, scale_range=(0.005, 0.05))
+    got, _ = T.run_case(afb, case)
+    rows = list(range(min(m, 2)))
+    ref = oracle.gemm(case, threads=8, rows=rows)
+    check_close(oracle, ref, got[rows], f"int4 g128 M={m}", floor_frac=1.0 if m > 16 else 0.05)
+
+
+def test_column_split_concatenates_exactly(afb):
+    case = T.make_case(256, 2048, 1024, seed=3)
+    whole, _ = T.run_case(afb, case)
+    parts = []
+    for r in range(2):
+        sl = slice(r * 1024, (r + 1) * 1024)
+        sub = T.Case(**{**case.__dict__, "n": 1024, "b": np.ascontiguousarray(case.b[sl]), "scale": np.ascontiguousarray(case.scale[sl])})
+        out, _ = T.run_case(afb, sub)
+        parts.append(out)
+    assert np.array_equal(np.concatenate(parts, axis=1), whole)

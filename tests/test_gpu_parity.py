@@ -1,0 +1,212 @@
+"""GPU parity tests: every kernel variant, through the C ABI, against the CPU oracle on the same
+seeded inputs.  Integer / byte work (unpack, dequant) must be bit-exact; bf16 outputs must be within
+max relative error 1e-2 of the oracle (denominators floored at a stated fraction of the tensor RMS)."""
+import os
+
+import numpy as np
+import pytest
+
+import afb_testlib as T
+import awesome_fusion_b200 as pkg
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+TOL = 1e-2            # max relative error on bf16 outputs
+FLOOR_FRAC = 0.05     # |ref| below this fraction of RMS(ref) is compared against the floor instead
+
+
+def check_close(oracle, ref, got_bf16, what, tol=TOL, floor_frac=FLOOR_FRAC):
+    floor = max(T.rms(ref) * floor_frac, 1e-30)
+    mx, nrms, worst = oracle.compare(ref, got_bf16, floor)
+    assert mx <= tol, f"{what}: max rel err {mx:.4g} at {worst} (ref {ref.reshape(-1)[worst]}, got " \
+                      f"{T.np_bf16_to_f32(got_bf16.reshape(-1)[worst:worst + 1])[0]}), nrms {nrms:.3g}"
+    return mx, nrms
+
+
+# ---------------------------------------------------------------- unpack + dequant: bit-exact
+@pytest.mark.parametrize("enc", [0, 1])
+@pytest.mark.parametrize("layout", [0, 1])
+def test_dequant_int8_all_byte_values(afb, oracle, enc, layout):
+    n, k = 64, 256
+    b = np.arange(n * k, dtype=np.uint32).astype(np.uint8).reshape(n, k)        # every byte value, many times
+    b = np.ascontiguousarray(b if layout == 1 else b.T)
+    case = T.Case(m=1, n=n, k=k, bits=8, group=0, layout=layout, enc=enc, scale_dtype=0, b=b,
+                  scale=np.ones(n, np.float32), ldb=b.shape[1])
+    d_b, d_s = afb.to_device(case.b), afb.to_device(case.scale)
+    d_o = afb.malloc(n * k * 2)
+    args = afb.make_args(d_o, d_b, d_b, d_s, 1, n, k, ldb=case.ldb, bits=8, encoding=enc, layout=layout)
+    afb.dequant_dump(args, d_o)
+    afb.device_sync()
+    got = afb.to_host(d_o, (n, k) if layout == 1 else (k, n), np.uint16)
+    for p in (d_b, d_s, d_o):
+        afb.free(p)
+    assert np.array_equal(got, oracle.dequant_bf16(case))
+
+
+@pytest.mark.parametrize("bits,group,enc,scale_dtype", [(4, 0, 0, 0), (4, 0, 1, 0), (4, 128, 0, 1), (4, 128, 1, 1), (4, 64, 0, 1),
+                                                       (8, 128, 0, 1), (8, 64, 1, 1), (4, 128, 0, 0)])
+def test_dequant_groups_and_int4(afb, oracle, bits, group, enc, scale_dtype):
+    case = T.make_case(1, 96, 512, bits=bits, group=group, enc=enc, scale_dtype=scale_dtype, seed=11, scale_range=(0.005, 0.05))
+    d_b, d_s = afb.to_device(case.b), afb.to_device(case.scale)
+    d_o = afb.malloc(case.n * case.k * 2)
+    args = afb.make_args(d_o, d_b, d_b, d_s, 1, case.n, case.k, ldb=case.ldb, bits=bits, encoding=enc, layout=1,
+                         scale_dtype=scale_dtype, group=group)
+    afb.dequant_dump(args, d_o)
+    afb.device_sync()
+    got = afb.to_host(d_o, (case.n, case.k), np.uint16)
+    for p in (d_b, d_s, d_o):
+        afb.free(p)
+    if group and scale_dtype == 0:
+        # fp32 scales are first rounded to bf16 by the kernels (the dequant contract multiplies two bf16 values)
+        case.scale = T.np_bf16_rne(case.scale); case.scale_dtype = 1
+    assert np.array_equal(got, oracle.dequant_bf16(case))
+
+
+# ---------------------------------------------------------------- naive variant: fp32 bit-exact with the oracle
+@pytest.mark.parametrize("bits,group,layout,enc", [(8, 0, 0, 1), (8, 0, 0, 0), (8, 0, 1, 0), (8, 128, 1, 1), (4, 0, 1, 0), (4, 128, 1, 0)])
+def test_naive_is_bit_exact_fp32(afb, oracle, bits, group, layout, enc):
+    case = T.make_case(7, 72, 384, bits=bits, group=group, layout=layout, enc=enc, seed=5)
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_NAIVE, c_f32=True)
+    assert np.array_equal(got.view(np.uint32), oracle.gemm(case).view(np.uint32))
+
+
+def test_naive_matches_reference_golden(afb):
+    g = np.load(os.path.join(GOLD, "gemm_rrr_real.npz"))
+    b = g["b"]                                     # [K,N] int8, the reference's layout
+    for enc in (0, 1):
+        stored = (b.astype(np.int16) + 128).astype(np.uint8) if enc else b.view(np.uint8)
+        case = T.Case(m=g["a_bf16"].shape[0], n=b.shape[1], k=b.shape[0], bits=8, group=0, layout=0, enc=enc, scale_dtype=0,
+                      a=g["a_bf16"], b=np.ascontiguousarray(stored), scale=g["scale"], ldb=b.shape[1])
+        got, _ = T.run_case(afb, case, variant=pkg.VARIANT_NAIVE, c_f32=True)
+        assert np.array_equal(got.view(np.uint32), g["c"].view(np.uint32))
+
+
+# ---------------------------------------------------------------- decode variant
+DECODE_SHAPES = [(1, 128, 256), (4, 256, 1024), (8, 136, 512), (9, 128, 64), (16, 4096, 4096), (3, 1000, 2048), (16, 264, 4096 + 64)]
+
+
+@pytest.mark.parametrize("m,n,k", DECODE_SHAPES)
+@pytest.mark.parametrize("enc", [0, 1])
+def test_decode_int8_per_channel(afb, oracle, m, n, k, enc):
+    case = T.make_case(m, n, k, bits=8, enc=enc, seed=m * 131 + n)
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_DECODE)
+    check_close(oracle, oracle.gemm(case, threads=8), got, f"decode int8 {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (16, 256, 2048), (5, 1000, 1024), (16, 4096, 4096)])
+@pytest.mark.parametrize("bits,group,scale_dtype", [(4, 0, 0), (4, 128, 1), (8, 128, 1), (4, 256, 1), (4, 128, 0), (4, 0, 1)])
+def test_decode_int4_and_groups(afb, oracle, m, n, k, bits, group, scale_dtype):
+    case = T.make_case(m, n, k, bits=bits, group=group, scale_dtype=scale_dtype, seed=k + m, scale_range=(0.005, 0.05))
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_DECODE)
+    check_close(oracle, oracle.gemm(case, threads=8), got, f"decode int{bits} g{group} {m}x{n}x{k}")
+
+
+def test_decode_is_deterministic_and_leaves_workspace_clean(afb, oracle):
+    case = T.make_case(16, 4096, 4096, seed=1)
+    first, _ = T.run_case(afb, case, variant=pkg.VARIANT_DECODE)
+    for _ in range(3):
+        again, _ = T.run_case(afb, case, variant=pkg.VARIANT_DECODE)
+        assert np.array_equal(first, again)
+
+
+# ---------------------------------------------------------------- prefill variant
+PREFILL_SHAPES = [(128, 256, 64), (128, 256, 512), (17, 128, 256), (256, 512, 1024), (300, 264, 320), (128, 128, 4096), (640, 1280, 2048)]
+
+
+@pytest.mark.parametrize("m,n,k", PREFILL_SHAPES)
+@pytest.mark.parametrize("enc", [0, 1])
+def test_prefill_int8_per_channel(afb, oracle, m, n, k, enc):
+    case = T.make_case(m, n, k, bits=8, enc=enc, seed=n + k)
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL)
+    check_close(oracle, oracle.gemm(case, threads=8), got, f"prefill int8 {m}x{n}x{k}")
+    assert afb.read_status()[0] == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (200, 520, 1024), (384, 1024, 2048)])
+@pytest.mark.parametrize("bits,group,scale_dtype", [(4, 0, 0), (4, 128, 1), (8, 128, 1), (4, 64, 1), (8, 0, 1)])
+def test_prefill_int4_and_groups(afb, oracle, m, n, k, bits, group, scale_dtype):
+    case = T.make_case(m, n, k, bits=bits, group=group, scale_dtype=scale_dtype, seed=7 * m + k, scale_range=(0.005, 0.05))
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL)
+    ref_exact = oracle.gemm(case, threads=8)
+    if group:
+        # tight check against the oracle fed with the SAME bf16-rounded weights the tensor cores see ...
+        check_close(oracle, oracle.gemm(case, round_w=True, threads=8), got, f"prefill int{bits} g{group} (rounded-weight oracle)")
+        # ... and the contract check against the pure-fp32 formula of host_ref.hpp:15-24, denominators floored at RMS
+        check_close(oracle, ref_exact, got, f"prefill int{bits} g{group} (host_ref formula)", floor_frac=1.0)
+    else:
+        check_close(oracle, ref_exact, got, f"prefill int{bits} {m}x{n}x{k}")
+    assert afb.read_status()[0] == 0
+
+
+# ---------------------------------------------------------------- known-answer cases (exact)
+@pytest.mark.parametrize("variant,m", [(pkg.VARIANT_DECODE, 16), (pkg.VARIANT_DECODE, 3), (pkg.VARIANT_PREFILL, 160), (pkg.VARIANT_NAIVE, 20)])
+@pytest.mark.parametrize("bits", [8, 4])
+def test_reference_style_integer_data_is_exact(afb, oracle, variant, m, bits):
+    """The reference validates on integers in {-2,-1,0,1} (random_gen.hpp:24,37,50): every product and
+    partial sum is exact, so any correct kernel must reproduce the oracle exactly after bf16 rounding."""
+    case = T.make_case(m, 256, 512, bits=bits, seed=2, integer_data=True)
+    got, _ = T.run_case(afb, case, variant=variant)
+    assert np.array_equal(got, T.np_bf16_rne(oracle.gemm(case)))
+
+
+@pytest.mark.parametrize("variant,m", [(pkg.VARIANT_DECODE, 8), (pkg.VARIANT_PREFILL, 128)])
+@pytest.mark.parametrize("bits", [8, 4])
+def test_one_hot_weights_select_activation_columns(afb, variant, m, bits):
+    n, k = 128, 256
+    case = T.make_case(m, n, k, bits=bits, seed=9)
+    q = np.zeros((n, k), np.int32)
+    sel = (np.arange(n) * 37) % k
+    q[np.arange(n), sel] = 1
+    u = q & (0xFF if bits == 8 else 0xF)
+    case.b = np.ascontiguousarray(u.astype(np.uint8) if bits == 8 else (u[:, 0::2] | (u[:, 1::2] << 4)).astype(np.uint8))
+    case.scale = np.ones(n, np.float32)
+    got, _ = T.run_case(afb, case, variant=variant)
+    assert np.array_equal(got, case.a[:, sel])      # scale 1, weight 1: C = selected columns of A, exactly
+
+
+@pytest.mark.parametrize("variant,m", [(pkg.VARIANT_DECODE, 4), (pkg.VARIANT_PREFILL, 128)])
+@pytest.mark.parametrize("bits,val", [(8, -128), (8, 127), (4, -8), (4, 7)])
+def test_extreme_weights_sign_extension(afb, oracle, variant, m, bits, val):
+    case = T.make_case(m, 128, 256, bits=bits, seed=4)
+    u = val & (0xFF if bits == 8 else 0xF)
+    case.b[:] = u if bits == 8 else (u | (u << 4))
+    case.q[:] = val
+    got, _ = T.run_case(afb, case, variant=variant)
+    check_close(oracle, oracle.gemm(case), got, f"all weights {val}")
+
+
+# ---------------------------------------------------------------- memory safety (no compute-sanitizer on this pool)
+@pytest.mark.parametrize("variant,m,n,k", [(pkg.VARIANT_DECODE, 5, 264, 512), (pkg.VARIANT_PREFILL, 130, 264, 256), (pkg.VARIANT_NAIVE, 5, 70, 64)])
+def test_guard_bytes_and_padding_untouched(afb, oracle, variant, m, n, k):
+    case = T.make_case(m, n, k, seed=6)
+    ldc = n + 24
+    got, raw = T.run_case(afb, case, variant=variant, ldc=ldc, guard=4096)
+    check_close(oracle, oracle.gemm(case), got, "padded C")
+    assert np.all(raw[:4096] == 0xCD) and np.all(raw[-4096:] == 0xCD)
+    body = raw[4096:-4096].view(np.uint16)
+    full = np.full(m * ldc, 0xCDCD, np.uint16); full[:body.size] = body
+    assert np.all(full.reshape(m, ldc)[:, n:].reshape(-1)[:(m - 1) * 24] == 0xCDCD)   # the ldc padding columns
+
+
+def test_unsupported_requests_return_status_not_fault(afb):
+    case = T.make_case(4, 128, 256, layout=0, seed=1)
+    dc = T.DeviceCase(afb, case)
+    try:
+        assert afb.gemm_launch_status(dc.args(variant=pkg.VARIANT_DECODE)) == -2
+        assert afb.gemm_launch_status(dc.args(variant=pkg.VARIANT_PREFILL)) == -2
+        a = dc.args(); a.k = 100; a.lda = 100
+        assert afb.gemm_launch_status(a) in (0, -2)      # auto falls back to the naive variant
+        a = dc.args(); a.ptr_a = 0
+        assert afb.gemm_launch_status(a) == -1
+        afb.device_sync()
+    finally:
+        dc.close()
+
+
+def test_host_pointer_entry_point(afb, oracle):
+    case = T.make_case(64, 256, 512, seed=12)
+    c = np.zeros((case.m, case.n), np.uint16)
+    args = afb.make_args(c, case.a, case.b, case.scale, case.m, case.n, case.k, ldb=case.ldb)
+    afb.gemm_host(args)
+    check_close(oracle, oracle.gemm(case), c, "afb_gemm_host")

@@ -1,0 +1,64 @@
+"""CPU tests of the host side: the C-ABI library loads and exports every declared symbol, argument
+validation and variant selection answer without a GPU, and the C++ driver + headers build."""
+import ctypes
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+import awesome_fusion_b200 as pkg
+from awesome_fusion_b200.capi import EXPORTS
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(pkg.library_path()):
+        pkg.build_library()
+    return pkg.load()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = open(os.path.join(ROOT, "include", "afb_capi.h")).read()
+    declared = set(re.findall(r"\b(afb_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    for name in sorted(declared):
+        assert hasattr(lib.lib, name), f"{name} is declared in afb_capi.h but not exported by libafb.so"
+    assert declared >= set(EXPORTS)
+
+
+def test_args_struct_layout_matches_reference_block():
+    # the first ten fields are the reference's packed kernarg block: 4 pointers then 6 x u32 (bfAintBGemm.cc:119-133)
+    A = pkg.GemmArgs
+    assert [A.ptr_c.offset, A.ptr_a.offset, A.ptr_b.offset, A.ptr_scale.offset] == [0, 8, 16, 24]
+    assert [A.m.offset, A.n.offset, A.k.offset, A.lda.offset, A.ldb.offset, A.ldc.offset] == [32, 36, 40, 44, 48, 52]
+    assert ctypes.sizeof(A) == 88
+
+
+def test_validation_without_gpu(lib):
+    a = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256)
+    v = ctypes.c_uint32()
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(a), ctypes.byref(v)) == 0 and v.value == pkg.VARIANT_DECODE
+    a.m = 512
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(a), ctypes.byref(v)) == 0 and v.value == pkg.VARIANT_PREFILL
+    a.b_layout = pkg.LAYOUT_ROW; a.ldb = 128       # the reference's [K,N] layout has no fast variant
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(a), ctypes.byref(v)) == 0 and v.value == pkg.VARIANT_NAIVE
+    a.variant = pkg.VARIANT_PREFILL
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(a), ctypes.byref(v)) == -2
+    bad = lib.make_args(0, 0x1000, 0x1000, 0x1000, 4, 128, 256)
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    bad = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256, bits=5)
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    bad = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256, lda=8)
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    bad = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256, group=96)
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    assert lib.lib.afb_status_string(-4).decode().startswith("a bounded")
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(pkg.AfbError):
+        pkg.Library(str(tmp_path / "nope.so"))
