@@ -25,6 +25,7 @@ EXPORTS = [
     "afb_event_record", "afb_event_sync", "afb_event_elapsed_ms", "afb_event_destroy", "afb_stream_create",
     "afb_stream_sync", "afb_stream_destroy", "afb_device_sync", "afb_gemm_launch", "afb_gemm_resolve_variant",
     "afb_gemm_host", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
+    "afb_ksplit_allreduce_launch", "afb_cast_f32_to_bf16",
     "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
 ]
 
@@ -105,9 +106,6 @@ class Library:
         L.afb_last_cuda_error_string.restype = ctypes.c_char_p
         L.afb_launch_count.restype = ctypes.c_ulonglong
         L.afb_version.restype = ctypes.c_char_p
-        for name in ("afb_ksplit_reduce_launch", "afb_gemm_launch_static"):
-            if hasattr(L, name):
-                getattr(L, name).restype = i32
 
     # ---- helpers -------------------------------------------------------------
     def check(self, status, what):

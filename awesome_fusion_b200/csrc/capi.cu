@@ -61,9 +61,9 @@ static int validate(const afb_gemm_args* a) {
 
 static int resolve(const afb_gemm_args& a, uint32_t* out) {
     uint32_t v = a.variant;
-    if (a.flags & AFB_FLAG_C_F32) {
-        if (v != AFB_VARIANT_AUTO && v != AFB_VARIANT_NAIVE) return AFB_ERR_UNSUPPORTED;
-        v = AFB_VARIANT_NAIVE;
+    if (a.flags & AFB_FLAG_C_F32) {  // fp32 output: the prefill variant (K-split partial sums) or the naive variant
+        if (v == AFB_VARIANT_DECODE) return AFB_ERR_UNSUPPORTED;
+        if (v == AFB_VARIANT_AUTO) v = (a.m > 16 && prefill_supports(a)) ? AFB_VARIANT_PREFILL : AFB_VARIANT_NAIVE;
     }
     if (v == AFB_VARIANT_AUTO) {
         if (a.m <= 16 && decode_supports(a)) v = AFB_VARIANT_DECODE;

@@ -237,8 +237,16 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
     for (uint32_t idx = tid; idx < p.m * kRowsPerCta; idx += kThreads) {
         const uint32_t mm = idx / kRowsPerCta, nn = nblk + (idx % kRowsPerCta);
         if (nn >= p.n) continue;
+        const float* src = p.ws + (size_t)mm * p.n + nn;
+        const size_t slice_stride = (size_t)p.m * p.n;
         float sum = 0.f;
-        for (uint32_t sl = 0; sl < p.slices; ++sl) sum += __ldcg(p.ws + ((size_t)sl * p.m + mm) * p.n + nn);
+        for (uint32_t sl = 0; sl < p.slices; sl += 8) {  // eight independent loads in flight, summed in slice order
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = sl + i < p.slices ? __ldcg(src + (sl + i) * slice_stride) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum += v[i];
+        }
         if (!GROUPED)
             sum *= p.scale_dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(p.scale)[nn])
                                                   : reinterpret_cast<const float*>(p.scale)[nn];

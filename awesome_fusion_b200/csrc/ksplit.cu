@@ -1,0 +1,200 @@
+// Row-parallel (K-split) exchange: the all-reduce of per-GPU partial sums as one kernel per GPU over
+// NVLink peer memory (reduce-scatter by peer loads, all-gather by peer stores), plus the fp32 -> bf16
+// cast that finishes the NCCL comparison path.  The reference is single-GPU (bfAintBGemm.cc:63) and has
+// no counterpart.  Only plain ld/st reach peer memory: no TMA, no multicast.
+//
+// Signals: every rank owns uint32 signals[2][AFB_MAX_RANKS]; rank q writes `epoch` into
+// signals[phase][q] of every rank.  Phase 0: "my partial of this epoch is complete" (the GEMM that
+// produced it precedes this kernel in stream order).  Phase 1: "I have stored my row block into your C".
+// Epochs only grow, so nothing is ever reset and a late reader cannot mistake an old signal.
+#include <cuda_bf16.h>
+#include "afb_internal.h"
+
+namespace afb {
+namespace {
+
+constexpr int kThreads = 512;
+
+struct ARParams {
+    const void* partial[AFB_MAX_RANKS];
+    uint16_t* c[AFB_MAX_RANKS];
+    uint32_t* signals[AFB_MAX_RANKS];
+    uint32_t rank, world, m, n, ld_partial, ldc, partial_f32, epoch;
+    unsigned long long wait_ns;
+    uint32_t* cta_done;   // local counter, zero between launches
+    int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits until signals[phase][q] >= epoch for every rank q.  One thread calls it.  false = gave up.
+__device__ bool wait_all(const uint32_t* my_signals, int phase, uint32_t world, uint32_t epoch, unsigned long long limit_ns) {
+    const unsigned long long t0 = now_ns();
+    for (uint32_t q = 0; q < world; ++q) {
+        const uint32_t* f = my_signals + phase * AFB_MAX_RANKS + q;
+        uint32_t spins = 0;
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+            if ((++spins & 0x3fu) == 0 && now_ns() - t0 > limit_ns) return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARParams p) {
+    __shared__ uint32_t s_ok;
+    __shared__ uint32_t s_last;
+    const uint32_t* my_sig = p.signals[p.rank];
+    if (threadIdx.x == 0) {
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 0 * AFB_MAX_RANKS + p.rank, p.epoch);
+        }
+        const bool ok = wait_all(my_sig, 0, p.world, p.epoch, p.wait_ns);
+        if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 10; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
+        s_ok = ok ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_ok) {
+        // rows [r0, r1) belong to this rank; 8 output columns (16 bytes of bf16) per thread per step
+        const uint32_t r0 = (uint32_t)((uint64_t)p.m * p.rank / p.world), r1 = (uint32_t)((uint64_t)p.m * (p.rank + 1) / p.world);
+        const uint32_t vec_per_row = p.n / 8;
+        const uint64_t total = (uint64_t)(r1 - r0) * vec_per_row;
+        for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (uint64_t)gridDim.x * kThreads) {
+            const uint32_t row = r0 + (uint32_t)(i / vec_per_row), col = (uint32_t)(i % vec_per_row) * 8;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (F32) {
+                uint4 lo[AFB_MAX_RANKS], hi[AFB_MAX_RANKS];
+#pragma unroll
+                for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                    if (q < (int)p.world) {
+                        const float* src = reinterpret_cast<const float*>(p.partial[q]) + (size_t)row * p.ld_partial + col;
+                        lo[q] = ld16(src); hi[q] = ld16(src + 4);
+                    }
+#pragma unroll
+                for (int q = 0; q < AFB_MAX_RANKS; ++q)   // fixed rank order: identical bits wherever it is computed
+                    if (q < (int)p.world) {
+                        acc[0] += __uint_as_float(lo[q].x); acc[1] += __uint_as_float(lo[q].y); acc[2] += __uint_as_float(lo[q].z); acc[3] += __uint_as_float(lo[q].w);
+                        acc[4] += __uint_as_float(hi[q].x); acc[5] += __uint_as_float(hi[q].y); acc[6] += __uint_as_float(hi[q].z); acc[7] += __uint_as_float(hi[q].w);
+                    }
+            } else {
+                uint4 v[AFB_MAX_RANKS];
+#pragma unroll
+                for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                    if (q < (int)p.world) v[q] = ld16(reinterpret_cast<const uint16_t*>(p.partial[q]) + (size_t)row * p.ld_partial + col);
+#pragma unroll
+                for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                    if (q < (int)p.world) {
+                        acc[0] += bf_lo(v[q].x); acc[1] += bf_hi(v[q].x); acc[2] += bf_lo(v[q].y); acc[3] += bf_hi(v[q].y);
+                        acc[4] += bf_lo(v[q].z); acc[5] += bf_hi(v[q].z); acc[6] += bf_lo(v[q].w); acc[7] += bf_hi(v[q].w);
+                    }
+            }
+            const uint4 out = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+#pragma unroll
+            for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                if (q < (int)p.world) *reinterpret_cast<uint4*>(p.c[q] + (size_t)row * p.ldc + col) = out;
+        }
+    }
+    // the last CTA to finish tells every rank that this rank's block is in place, then waits for theirs
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t old = atomicAdd(p.cta_done, 1u);
+        s_last = old == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        *p.cta_done = 0u;
+        __threadfence_system();
+        if (s_ok) {   // after a timeout nothing was stored: do not claim completion
+            for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 1 * AFB_MAX_RANKS + p.rank, p.epoch);
+            const bool ok = wait_all(my_sig, 1, p.world, p.epoch, p.wait_ns);
+            if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 11; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(uint16_t* __restrict__ dst, const float* __restrict__ src, uint32_t rows,
+                                                            uint32_t cols, uint32_t ld_dst, uint32_t ld_src) {
+    const uint32_t vec_per_row = cols / 8;
+    const uint64_t total = (uint64_t)rows * vec_per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (uint64_t)gridDim.x * 256) {
+        const uint32_t r = (uint32_t)(i / vec_per_row), c = (uint32_t)(i % vec_per_row) * 8;
+        const float4 a = *reinterpret_cast<const float4*>(src + (size_t)r * ld_src + c);
+        const float4 b = *reinterpret_cast<const float4*>(src + (size_t)r * ld_src + c + 4);
+        *reinterpret_cast<uint4*>(dst + (size_t)r * ld_dst + c) =
+            make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+    }
+}
+
+uint32_t* g_cta_done[32] = {nullptr};
+
+}  // namespace
+}  // namespace afb
+
+using namespace afb;
+
+extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* stream) {
+    if (!a) return AFB_ERR_BAD_ARG;
+    if (a->world == 0 || a->world > AFB_MAX_RANKS || a->rank >= a->world) return AFB_ERR_BAD_ARG;
+    if (a->m == 0 || a->n == 0 || a->n % 8 || a->ldc % 8 || a->ld_partial % 8 || a->ld_partial < a->n || a->ldc < a->n) return AFB_ERR_BAD_ARG;
+    if (a->epoch == 0 || a->reserved != 0) return AFB_ERR_BAD_ARG;
+    for (uint32_t q = 0; q < a->world; ++q) {
+        if (!a->partial[q] || !a->c[q] || !a->signals[q]) return AFB_ERR_BAD_ARG;
+        if ((uintptr_t)a->partial[q] % 16 || (uintptr_t)a->c[q] % 16) return AFB_ERR_BAD_ARG;
+    }
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    if (!g_cta_done[ctx->device]) {
+        cudaError_t e = cudaMalloc(&g_cta_done[ctx->device], sizeof(uint32_t));
+        if (e != cudaSuccess) return cuda_fail(e);
+        e = cudaMemset(g_cta_done[ctx->device], 0, sizeof(uint32_t));
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    ARParams p;
+    for (int q = 0; q < AFB_MAX_RANKS; ++q) {
+        p.partial[q] = q < (int)a->world ? a->partial[q] : nullptr;
+        p.c[q] = q < (int)a->world ? reinterpret_cast<uint16_t*>(a->c[q]) : nullptr;
+        p.signals[q] = q < (int)a->world ? a->signals[q] : nullptr;
+    }
+    p.rank = a->rank; p.world = a->world; p.m = a->m; p.n = a->n; p.ld_partial = a->ld_partial; p.ldc = a->ldc;
+    p.partial_f32 = a->partial_f32; p.epoch = a->epoch;
+    p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
+    p.cta_done = g_cta_done[ctx->device];
+    p.status = ctx->status;
+    const int grid = ctx->sm_count;   // one CTA per SM: all CTAs are co-resident, so the last-CTA hand-off cannot starve
+    if (a->partial_f32) ksplit_allreduce_kernel<true><<<grid, kThreads, 0, (cudaStream_t)stream>>>(p);
+    else                ksplit_allreduce_kernel<false><<<grid, kThreads, 0, (cudaStream_t)stream>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
+extern "C" int afb_cast_f32_to_bf16(void* dst, const void* src, uint32_t rows, uint32_t cols, uint32_t ld_dst, uint32_t ld_src, void* stream) {
+    if (!dst || !src || rows == 0 || cols == 0 || cols % 8 || ld_dst % 8 || ld_src % 4) return AFB_ERR_BAD_ARG;
+    if ((uintptr_t)dst % 16 || (uintptr_t)src % 16) return AFB_ERR_BAD_ARG;
+    if (!current_ctx()) return AFB_ERR_NOT_INIT;
+    cast_f32_bf16_kernel<<<592, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<uint16_t*>(dst), reinterpret_cast<const float*>(src), rows, cols, ld_dst, ld_src);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}

@@ -28,8 +28,7 @@ constexpr int kStagesB = 3;   // converted-B ring
 constexpr int kConvWarps = 8;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 32 * (2 + kEpiWarps + kConvWarps);  // 448
-constexpr int kFirstEpiWarp = 2;
-constexpr int kFirstConvWarp = 2 + kEpiWarps;
+constexpr int kFirstConvWarp = 2 + kEpiWarps;   // warps 2 .. 2+kEpiWarps-1 are the epilogue
 
 struct PrefillParams {
     uint16_t* c;
@@ -37,6 +36,7 @@ struct PrefillParams {
     uint32_t m, n, k, ldc;
     uint32_t enc, scale_dtype, group;
     uint32_t m_tiles, n_tiles;
+    uint32_t c_f32;     // 1: C is fp32 (partial sums of a K-split), 0: bf16
     int32_t* status;
 };
 
@@ -193,8 +193,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else if (warp < kFirstConvWarp) {
         // ======================= epilogue =======================
-        const int et = threadIdx.x - kFirstEpiWarp * 32;     // 0..127
-        const uint32_t lane_group = (uint32_t)(warp & 3);    // TMEM lanes this warp may read
+            const uint32_t lane_group = (uint32_t)(warp & 3);    // TMEM lanes this warp may read
         uint32_t it = 0;
         for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const uint32_t as = it & 1u, ap = (it >> 1) & 1u;
@@ -206,6 +205,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ptx::tc_fence_after_sync();
             const uint32_t row = m0 + lane_group * 32 + lane;
             uint16_t* crow = p.c + (size_t)row * p.ldc + n0;
+            float* crow32 = reinterpret_cast<float*>(p.c) + (size_t)row * p.ldc + n0;
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
                 uint32_t r[32];
@@ -216,17 +216,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (int q = 0; q < 4; ++q) {
                         const uint32_t col = n0 + ch * 32 + q * 8;
                         if (col < p.n) {
-                            float sc[8];
-                            if (!GROUPED) load_scale8(p.scale, p.scale_dtype, col, sc);  // same address in all lanes: one broadcast
-                            uint32_t o[4];
+                            float v[8];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                float v0 = __uint_as_float(r[q * 8 + 2 * e]), v1 = __uint_as_float(r[q * 8 + 2 * e + 1]);
-                                if (!GROUPED) { v0 *= sc[2 * e]; v1 *= sc[2 * e + 1]; }
-                                const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-                                o[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[q * 8 + e]);
+                            if (!GROUPED) {
+                                float sc[8];
+                                load_scale8(p.scale, p.scale_dtype, col, sc);  // same address in all lanes: one broadcast
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] *= sc[e];
                             }
-                            *reinterpret_cast<uint4*>(crow + ch * 32 + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                            if (p.c_f32) {
+                                *reinterpret_cast<float4*>(crow32 + ch * 32 + q * 8) = make_float4(v[0], v[1], v[2], v[3]);
+                                *reinterpret_cast<float4*>(crow32 + ch * 32 + q * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                            } else {
+                                uint32_t o[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                                    o[e] = *reinterpret_cast<const uint32_t*>(&h);
+                                }
+                                *reinterpret_cast<uint4*>(crow + ch * 32 + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                            }
                         }
                     }
                 }
@@ -252,7 +262,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             auto load_scale = [&](int itx, uint32_t gidx) -> uint32_t {
                 const uint32_t rowi = (uint32_t)(itx * (kConvWarps * 32) + cid) / kPiecesPerRow;
                 const uint32_t nn = n0 + rowi;
-                if (nn >= p.n || gidx >= groups_per_row) return 0u;
+                if (nn >= p.n || gidx >= groups_per_row) return (uint32_t)0;
                 return bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
             };
             if (GROUPED) {
@@ -351,6 +361,7 @@ int launch_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
     p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
     p.m_tiles = (a.m + BM - 1) / BM;
     p.n_tiles = (a.n + BN - 1) / BN;
+    p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
     p.status = ctx->status;
     auto kern = prefill_kernel<BITS, GROUPED, BN>;
     static bool attr_set = false;  // per template instance
@@ -378,7 +389,7 @@ bool prefill_supports(const afb_gemm_args& a) {
     if (a.lda % 8 || a.ldc % 8) return false;
     const uint64_t ld_bytes = (uint64_t)a.ldb * a.b_bits / 8;
     if (ld_bytes % 16) return false;
-    if ((uintptr_t)a.ptr_a % 16 || (uintptr_t)a.ptr_b % 16 || (uintptr_t)a.ptr_c % 16) return false;
+    if ((uintptr_t)a.ptr_a % 16 || (uintptr_t)a.ptr_b % 16 || (uintptr_t)a.ptr_c % 16 || (uintptr_t)a.ptr_scale % 16) return false;
     if (a.group_size) {
         if (a.group_size % BK || a.k % a.group_size) return false;
         if (a.scale_dtype != AFB_SCALE_BF16) return false;  // the dequant contract is bf16_rn(q * bf16 scale)

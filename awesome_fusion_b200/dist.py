@@ -1,0 +1,245 @@
+"""Sharding of the GEMM across the GPUs of one box: one process per GPU (torch.distributed for the
+rendezvous and, on the comparison path, NCCL).
+
+* column-parallel (N-split): rank r owns B[r*N/p:(r+1)*N/p, :], the matching scales and C[:, same];
+  A is replicated.  Independent units, no collective.
+* row-parallel (K-split): rank r owns A[:, K_r] and B[:, K_r]; per-channel scales do not depend on k,
+  so every rank applies them to its own partial sum, and the partial sums are added across ranks:
+    - "fused": afb_ksplit_allreduce_launch, one kernel per GPU over NVLink peer memory (buffers shared
+      between the processes with CUDA IPC handles);
+    - "nccl":  fp32 partial sums, torch.distributed.all_reduce, then afb_cast_f32_to_bf16.
+
+The partition arithmetic (`split_range`, `column_shard`, `k_shard`) is plain Python so that it can be
+tested on CPU ranks.
+"""
+import ctypes
+
+MAX_RANKS = 8
+
+
+def split_range(total, world, rank, multiple=1):
+    """[lo, hi) of `total` owned by `rank`: equal shares of whole `multiple`-sized units, remainder to the first ranks."""
+    if total % multiple:
+        raise ValueError(f"{total} is not a multiple of {multiple}")
+    units = total // multiple
+    base, rem = divmod(units, world)
+    lo = rank * base + min(rank, rem)
+    hi = lo + base + (1 if rank < rem else 0)
+    return lo * multiple, hi * multiple
+
+
+def column_shard(n, world, rank):
+    """Output channels of a column-parallel GEMM owned by `rank` (multiples of 8: 16-byte rows of bf16 C)."""
+    return split_range(n, world, rank, 8)
+
+
+def k_shard(k, world, rank, bits=8, group=0):
+    """K range of a row-parallel GEMM owned by `rank`: whole 64-wide K steps (128 for 4-bit), whole scale groups."""
+    mult = 64 if bits == 8 else 128
+    if group:
+        mult = max(mult, group)
+    return split_range(k, world, rank, mult)
+
+
+class AllReduceArgs(ctypes.Structure):
+    """``afb_allreduce_args`` of include/afb_capi.h."""
+    _fields_ = [("partial", ctypes.c_void_p * MAX_RANKS), ("c", ctypes.c_void_p * MAX_RANKS), ("signals", ctypes.c_void_p * MAX_RANKS),
+                ("rank", ctypes.c_uint32), ("world", ctypes.c_uint32), ("m", ctypes.c_uint32), ("n", ctypes.c_uint32),
+                ("ld_partial", ctypes.c_uint32), ("ldc", ctypes.c_uint32), ("partial_f32", ctypes.c_uint32), ("epoch", ctypes.c_uint32),
+                ("wait_ms", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+
+
+class PeerExchange:
+    """Buffers of the fused K-split all-reduce, shared between the ranks of one box by CUDA IPC.
+
+    Each rank allocates (through the C ABI, so the allocation is a whole cudaMalloc block) its partial-sum
+    buffer, its result buffer C and its signal words, exports the three handles, and maps every peer's."""
+
+    def __init__(self, lib, torch_dist, rank, world, m, n, partial_f32=True, wait_ms=2000):
+        self.lib, self.rank, self.world, self.m, self.n = lib, rank, world, m, n
+        self.partial_f32 = partial_f32
+        self.wait_ms = wait_ms
+        self.epoch = 0
+        pbytes = m * n * (4 if partial_f32 else 2)
+        self.partial = lib.malloc(pbytes)
+        self.c = lib.malloc(m * n * 2)
+        self.signals = lib.malloc(2 * MAX_RANKS * 4)
+        lib.memset(self.signals, 0, 2 * MAX_RANKS * 4)
+        lib.device_sync()
+        self._imported = []
+        self.partials, self.cs, self.sigs = [None] * world, [None] * world, [None] * world
+        self.ok = True
+        if world == 1:
+            self.partials[0], self.cs[0], self.sigs[0] = self.partial, self.c, self.signals
+            return
+        # No rank may raise between the collectives below (the others would wait for it for ever):
+        # failures are recorded, exchanged, and every rank reaches the same verdict.
+        try:
+            mine = (lib.ipc_export(self.partial), lib.ipc_export(self.c), lib.ipc_export(self.signals))
+        except Exception as e:  # noqa: BLE001
+            mine, self.error = None, str(e)
+        everyone = [None] * world
+        torch_dist.all_gather_object(everyone, mine)
+        if any(h is None for h in everyone):
+            self.ok = False
+        else:
+            try:
+                for q, (hp, hc, hs) in enumerate(everyone):
+                    if q == rank:
+                        self.partials[q], self.cs[q], self.sigs[q] = self.partial, self.c, self.signals
+                    else:
+                        ptrs = []
+                        for h in (hp, hc, hs):
+                            ptrs.append(lib.ipc_import(h))
+                            self._imported.append(ptrs[-1])
+                        self.partials[q], self.cs[q], self.sigs[q] = ptrs
+            except Exception as e:  # noqa: BLE001
+                self.ok, self.error = False, str(e)
+        verdicts = [None] * world
+        torch_dist.all_gather_object(verdicts, self.ok)
+        self.ok = all(verdicts)
+
+    def args(self):
+        a = AllReduceArgs()
+        for q in range(self.world):
+            a.partial[q], a.c[q], a.signals[q] = self.partials[q], self.cs[q], self.sigs[q]
+        a.rank, a.world, a.m, a.n = self.rank, self.world, self.m, self.n
+        a.ld_partial, a.ldc, a.partial_f32 = self.n, self.n, 1 if self.partial_f32 else 0
+        a.wait_ms, a.reserved = self.wait_ms, 0
+        return a
+
+    def allreduce(self, stream=None):
+        self.epoch += 1
+        a = self.args()
+        a.epoch = self.epoch
+        self.lib.lib.afb_ksplit_allreduce_launch.argtypes = [ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
+        self.lib.check(self.lib.lib.afb_ksplit_allreduce_launch(ctypes.byref(a), stream), "afb_ksplit_allreduce_launch")
+
+    def close(self):
+        self.lib.device_sync()
+        for p in self._imported:
+            self.lib.ipc_release(p)
+        for p in (self.partial, self.c, self.signals):
+            self.lib.free(p)
+
+
+def cast_f32_to_bf16(lib, dst, src, rows, cols, stream=None):
+    f = lib.lib.afb_cast_f32_to_bf16
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]
+    lib.check(f(dst, src, rows, cols, cols, cols, stream), "afb_cast_f32_to_bf16")
+
+
+class ShardedMLP:
+    """The sharded benchmark step: column-parallel up-projection + row-parallel down-projection (int8, per-channel).
+
+    exchange: "fused" | "nccl" | "auto" (fused when the box shares memory between the processes, else nccl).
+    partial:  "f32" (exact, ordered sum) | "bf16" (half the NVLink bytes; each partial rounded once)."""
+
+    def __init__(self, lib, torch, rank=0, world=1, exchange="auto", partial="f32", m=4096, up=(28672, 8192), down=(8192, 28672), seed=0):
+        import awesome_fusion_b200 as pkg
+        self.lib, self.torch, self.rank, self.world, self.m = lib, torch, rank, world, m
+        self.pkg = pkg
+        dev = torch.device("cuda", torch.cuda.current_device())
+        up_n, up_k = up
+        down_n, down_k = down
+        n_lo, n_hi = column_shard(up_n, world, rank)
+        k_lo, k_hi = k_shard(down_k, world, rank)
+        self.up_n_local, self.up_k = n_hi - n_lo, up_k
+        self.down_n, self.down_k_local = down_n, k_hi - k_lo
+        g = torch.Generator(device=dev); g.manual_seed(seed)            # replicated tensors: the same seed on every rank
+        gr = torch.Generator(device=dev); gr.manual_seed(seed + 1 + rank)  # rank-local tensors: seed + 1 + rank
+        self.a_up = torch.randn((m, up_k), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        self.b_up = torch.randint(-127, 128, (self.up_n_local, up_k), generator=gr, device=dev, dtype=torch.int8)
+        self.s_up = torch.rand((self.up_n_local,), generator=gr, device=dev) * 0.009 + 0.001
+        self.c_up = torch.empty((m, self.up_n_local), device=dev, dtype=torch.bfloat16)
+        self.a_down = torch.randn((m, self.down_k_local), generator=gr, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        self.b_down = torch.randint(-127, 128, (down_n, self.down_k_local), generator=gr, device=dev, dtype=torch.int8)
+        self.s_down = torch.rand((down_n,), generator=g, device=dev) * 0.009 + 0.001   # scales are per output channel: replicated
+        self.flops_per_step_global = 2.0 * m * up_n * up_k + 2.0 * m * down_n * down_k
+        self.args_up = lib.make_args(self.c_up, self.a_up, self.b_up, self.s_up, m, self.up_n_local, up_k)
+        self.px = None
+        if world == 1:
+            self.exchange_name = "none (1 GPU)"
+            self.c_down = torch.empty((m, down_n), device=dev, dtype=torch.bfloat16)
+            self.args_down = lib.make_args(self.c_down, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local)
+            return
+        import torch.distributed as tdist
+        self.tdist = tdist
+        mode = exchange
+        if mode == "auto":
+            mode = "fused"
+        if mode == "fused":
+            self.px = PeerExchange(lib, tdist, rank, world, m, down_n, partial_f32=(partial == "f32"))
+            if not self.px.ok:
+                why = getattr(self.px, "error", "a peer could not share its memory")
+                self.px.close(); self.px = None
+                if exchange == "fused":
+                    raise pkg.AfbError(-3, "peer-memory exchange unavailable", why)
+                if rank == 0:
+                    print(f"peer memory unavailable ({why}); using the NCCL exchange", flush=True)
+                mode = "nccl"
+        if mode == "fused":
+            self.exchange_name = f"fused peer-memory all-reduce ({partial} partial sums)"
+            flags = 0 if partial == "bf16" else pkg.FLAG_C_F32
+            self.args_down = lib.make_args(self.px.partial, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local, flags=flags)
+        else:
+            self.exchange_name = "nccl all-reduce of fp32 partial sums + cast"
+            self.partial32 = torch.empty((m, down_n), device=dev, dtype=torch.float32)
+            self.c_down = torch.empty((m, down_n), device=dev, dtype=torch.bfloat16)
+            self.args_down = lib.make_args(self.partial32, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local,
+                                           flags=pkg.FLAG_C_F32)
+
+    def step(self, stream, events=None):
+        lib = self.lib
+        if events:
+            events[0].record()
+        lib.gemm_launch(self.args_up, stream)
+        if events:
+            events[1].record()
+        lib.gemm_launch(self.args_down, stream)
+        if self.world > 1:
+            if self.px is not None:
+                self.px.allreduce(stream)
+            else:
+                self.tdist.all_reduce(self.partial32)
+                cast_f32_to_bf16(lib, self.c_down.data_ptr(), self.partial32.data_ptr(), self.m, self.down_n, stream)
+        if events:
+            events[2].record()
+
+    def result_down(self):
+        """bf16 result of the down-projection as a torch tensor on the host (tests)."""
+        torch = self.torch
+        if self.px is not None:
+            import numpy as np
+            arr = self.lib.to_host(self.px.c, (self.m, self.down_n), np.uint16)
+            return torch.from_numpy(arr.view(np.int16)).view(torch.bfloat16)
+        return self.c_down.cpu()
+
+    def e2e(self, steps=5, warmup=2):
+        """The same step through afb_gemm_host: pinned host inputs, H2D + launch + D2H inside the timed region.
+        (At N>1 the row-parallel partial sums come back to the host as this rank's fp32 partial: the exchange is
+        timed in the device-resident figure, not here.)"""
+        torch, lib = self.torch, self.lib
+        host = {}
+        for name in ("a_up", "b_up", "s_up", "a_down", "b_down", "s_down"):
+            host[name] = getattr(self, name).cpu().pin_memory()
+        c_up = torch.empty((self.m, self.up_n_local), dtype=torch.bfloat16).pin_memory()
+        c_down = torch.empty((self.m, self.down_n), dtype=torch.bfloat16).pin_memory()
+        a1 = lib.make_args(c_up, host["a_up"], host["b_up"], host["s_up"], self.m, self.up_n_local, self.up_k)
+        a2 = lib.make_args(c_down, host["a_down"], host["b_down"], host["s_down"], self.m, self.down_n, self.down_k_local)
+        h2d = sum(host[k].numel() * host[k].element_size() for k in host)
+        d2h = c_up.numel() * 2 + c_down.numel() * 2
+        import time
+
+        def one():
+            lib.gemm_host(a1)
+            lib.gemm_host(a2)
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) / steps * 1e3
+        return {"ms": ms, "h2d": h2d, "d2h": d2h}

@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the bfAintBGemm path: bf16 x int GEMM TFLOP/s (and HBM GB/s for the decode cases).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Headline workload ("sharded-mlp", every N): the two 70B-class layers of the sharded configuration,
+one step = one column-parallel up-projection (M=4096, N=28672 split over the GPUs, K=8192) followed by
+one row-parallel down-projection (M=4096, N=8192, K=28672 split over the GPUs) whose partial sums are
+combined across the GPUs.  int8 weights, per-channel fp32 scales, bf16 activations and outputs.
+At N=1 both GEMMs run whole on one GPU (strong scaling: total work is fixed as N grows).
+At N=1 the same run also measures the single-GPU configurations (decode, prefill, group-wise int4)
+and reports them under "cases"; --workload picks one of them as the only thing to run (used for
+profiling).  One JSON line is printed by rank 0.
+
+Launch for N>1:  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1
+                 --master-port P bench.py --gpus N --steps K --warmup W
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bf16 x int GEMM throughput (2*M*N*K / time)"
+NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK)
+    d["_source"] = "fallback"
+    return d
+
+
+# ----------------------------------------------------------------------------------------
+# algorithmic work (the reference's own formulas, bfAintBGemm.cc:187-188, plus the scale term; units 1e12 / 1e9)
+# ----------------------------------------------------------------------------------------
+def gemm_flops(m, n, k):
+    return 2.0 * m * n * k
+
+
+def gemm_bytes(m, n, k, bits, group):
+    scale_bytes = 2 * n * (k // group) if group else 4 * n
+    return 2 * m * k + n * k * bits // 8 + scale_bytes + 2 * m * n
+
+
+# ----------------------------------------------------------------------------------------
+# clocks during the timed region
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return res
+        time.sleep(0.15)
+        self.proc.terminate()   # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            sm.sort()
+            res.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return res
+
+
+# ----------------------------------------------------------------------------------------
+# device-resident problem instances (torch owns the memory; the kernels are ours, through the C ABI)
+# ----------------------------------------------------------------------------------------
+class Gemm:
+    """One GEMM with synthetic inputs of the benchmark distributions, `copies` distinct weight buffers to rotate over."""
+
+    def __init__(self, lib, torch, m, n, k, *, bits=8, group=0, seed=0, copies=1, variant=0, lda=None, c_f32=False, a=None):
+        import awesome_fusion_b200 as pkg
+        self.lib, self.m, self.n, self.k, self.bits, self.group = lib, m, n, k, bits, group
+        dev = torch.device("cuda", torch.cuda.current_device())
+        g = torch.Generator(device=dev); g.manual_seed(seed)
+        self.a = a if a is not None else torch.randn((m, k), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        self.b, self.s, self.args = [], [], []
+        self.c = torch.empty((m, n), device=dev, dtype=torch.float32 if c_f32 else torch.bfloat16)
+        for _ in range(copies):
+            if bits == 8:
+                b = torch.randint(-127, 128, (n, k), generator=g, device=dev, dtype=torch.int8)
+            else:
+                q = torch.randint(-8, 8, (n, k), generator=g, device=dev, dtype=torch.int8)
+                b = ((q[:, 0::2] & 0xF) | (q[:, 1::2] << 4)).to(torch.uint8).contiguous()
+                del q
+            if group:
+                s = (torch.rand((n, k // group), generator=g, device=dev) * 0.045 + 0.005).to(torch.bfloat16)
+            else:
+                s = torch.rand((n,), generator=g, device=dev) * 0.009 + 0.001
+            self.b.append(b); self.s.append(s)
+            self.args.append(lib.make_args(self.c, self.a, b, s, m, n, k, lda=lda or self.a.stride(0), bits=bits, group=group,
+                                           scale_dtype=pkg.SCALE_BF16 if group else pkg.SCALE_F32, variant=variant,
+                                           flags=pkg.FLAG_C_F32 if c_f32 else 0))
+        self.flops = gemm_flops(m, n, k)
+        self.bytes = gemm_bytes(m, n, k, bits, group)
+        self.i = 0
+
+    def launch(self, stream):
+        self.lib.gemm_launch(self.args[self.i], stream)
+        self.i = (self.i + 1) % len(self.args)
+
+
+def time_launches(torch, fn, steps, warmup):
+    """ms per call of fn(), CUDA events on torch's current stream (the stream fn launches on)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def single_case(lib, torch, name, m, n, k, bits, group, peaks, steps, warmup):
+    """One single-GPU configuration: kernel-only timing with the weights rotated over more than L2's worth of buffers."""
+    stream = torch.cuda.current_stream().cuda_stream
+    wbytes = n * k * bits // 8
+    copies = max(1, min(24, -(-400_000_000 // wbytes)))   # >= 400 MB of distinct weights (L2 is 126 MB)
+    op = Gemm(lib, torch, m, n, k, bits=bits, group=group, seed=1, copies=copies)
+    ms = time_launches(torch, lambda: op.launch(stream), steps, warmup)
+    import awesome_fusion_b200 as pkg
+    variant = {pkg.VARIANT_DECODE: "decode", pkg.VARIANT_PREFILL: "prefill", pkg.VARIANT_NAIVE: "naive"}[lib.resolve_variant(op.args[0])]
+    tf, gb = op.flops / ms / 1e9, op.bytes / ms / 1e6
+    ai = op.flops / op.bytes
+    bound = "hbm" if ai < peaks["bf16_tflops"] * 1e3 / peaks["hbm_gbs"] else "tensor"
+    res = {"name": name, "variant": variant, "m": m, "n": n, "k": k, "bits": bits, "group": group, "us": round(ms * 1e3, 2),
+           "tflops": round(tf, 2), "gbs": round(gb, 1), "bound": bound, "weight_buffers_rotated": copies,
+           "frac_of_measured": round(gb / peaks["hbm_gbs"] if bound == "hbm" else tf / peaks["bf16_tflops"], 4),
+           "frac_of_nominal": round(gb / NOMINAL["hbm_gbs"] if bound == "hbm" else tf / NOMINAL["bf16_tflops"], 4)}
+    del op
+    torch.cuda.empty_cache()
+    return res
+
+
+SINGLE_CASES = {
+    "decode-m1": (1, 4096, 4096, 8, 0), "decode-m4": (4, 4096, 4096, 8, 0), "decode-m16": (16, 4096, 4096, 8, 0),
+    "prefill": (2048, 11008, 4096, 8, 0),
+    "int4-m1": (1, 28672, 8192, 4, 128), "int4-m16": (16, 28672, 8192, 4, 128), "int4-m128": (128, 28672, 8192, 4, 128),
+    "int4-m4096": (4096, 28672, 8192, 4, 128),
+    "cpu-checkable": (256, 1024, 1024, 8, 0),
+}
+
+
+# ----------------------------------------------------------------------------------------
+# CPU arm: the reference's own gemm_rrr (host_ref.hpp) compiled into oracle/_ref, else the oracle port
+# ----------------------------------------------------------------------------------------
+def cpu_arm(seconds_target=12.0):
+    """Times the reference's CPU GEMM on a bounded sample of the headline workload: `rows` rows of C of the
+    up-projection (N=28672, K=8192, all of N and K), one row-range per host thread.  Returns (tflops, info)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import afb_testlib as T
+    cores = os.cpu_count() or 1
+    n, k = 28672, 8192
+    rng = np.random.default_rng(0)
+    ref = T.load_hostref()
+    kind = "reference" if ref is not None else "port"
+    # about 0.2 GFLOP/s per thread for the reference loop (B is read with stride N), 1.8 for the port
+    per_thread_gflops = 0.2 if ref is not None else 1.5
+    rows_per_thread = max(1, int(seconds_target * per_thread_gflops * 1e9 / (2.0 * n * k)))
+    rows = rows_per_thread * cores
+    a = rng.standard_normal((rows, k), dtype=np.float32)
+    if ref is not None:
+        b = rng.integers(-127, 128, size=(k, n), dtype=np.int8).astype(np.float32)
+        s = rng.uniform(0.001, 0.01, n).astype(np.float32)
+        run = lambda: ref.gemm_rrr(a, b, s, threads=cores)
+    else:
+        orc = T.load_oracle()
+        case = T.make_case(rows, n, k, seed=0)
+        run = lambda: orc.gemm(case, threads=cores)
+    t0 = time.perf_counter()
+    run()
+    dt = time.perf_counter() - t0
+    info = {"kind": kind, "cores": cores, "seconds": round(dt, 2),
+            "sample": f"{rows} of 4096 rows of C of the up-projection (M x 28672 x 8192, int8 per-channel), all N and K, "
+                      f"{rows_per_thread} row(s) per host thread; the down-projection has the same FLOPs"}
+    return 2.0 * rows * n * k / dt / 1e12, info, dt
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    # each step is one bounded sample; keep the whole run within a few minutes
+    per = max(2.0, min(12.0, 150.0 / (steps + warm)))
+    for _ in range(warm):
+        cpu_arm(per)
+    vals, total = [], 0.0
+    info = None
+    for _ in range(steps):
+        v, info, dt = cpu_arm(per)
+        vals.append(v); total += dt
+    v = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+            "ms_per_step": total / steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint8->fp32",
+            "data": "synthetic", "config": headline_config(args.gpus),
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+def headline_config(n_gpus):
+    return {"workload": "sharded-mlp: column-parallel up-proj 4096 x 28672 x 8192 + row-parallel down-proj 4096 x 8192 x 28672, "
+                        "int8 weights [N,K], per-channel fp32 scales, bf16 in/out, fp32 accumulate",
+            "m": 4096, "up": [28672, 8192], "down": [8192, 28672], "parallelism": f"tp{n_gpus} (N-split up, K-split down)",
+            "l2": "inputs larger than L2 (weights 235 MB per GEMM)", "flops_per_step": 2 * gemm_flops(4096, 28672, 8192)}
+
+
+# ----------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import awesome_fusion_b200 as pkg
+    from awesome_fusion_b200 import dist as afb_dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch N>1 with torch.distributed.run (see the docstring)")
+    torch.cuda.set_device(local)
+    lib = pkg.load()          # raises when libafb.so is missing: no fallback
+    lib.init(local)
+    peaks = measured_peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    steps, warm = args.steps, max(3, args.warmup)
+
+    if args.workload != "sharded-mlp":
+        m, n, k, bits, group = SINGLE_CASES[args.workload]
+        res = single_case(lib, torch, args.workload, m, n, k, bits, group, peaks, steps, warm)
+        print(json.dumps({"workload": args.workload, **res, "status": lib.read_status()}))
+        return 0
+
+    if world > 1:
+        import torch.distributed as tdist
+        tdist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    mlp = afb_dist.ShardedMLP(lib, torch, rank=rank, world=world, exchange=args.exchange)
+
+    def barrier():
+        if world > 1:
+            tdist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warm):
+        mlp.step(stream)
+    barrier()
+    launches0 = lib.launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    e0.record()
+    for i in range(steps):
+        mlp.step(stream, events=kev[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1) / steps
+    launches = lib.launch_count() - launches0
+    up_ms = sum(a.elapsed_time(b) for a, b, _ in kev) / steps
+    down_ms = sum(b.elapsed_time(c) for _, b, c in kev) / steps     # includes the exchange at N > 1
+    t = torch.tensor([ms, up_ms, down_ms, float(launches)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        tmax = t.clone(); tdist.all_reduce(tmax, op=tdist.ReduceOp.MAX)
+        tsum = t.clone(); tdist.all_reduce(tsum, op=tdist.ReduceOp.SUM)
+        ms, up_ms, down_ms = tmax[0].item(), tmax[1].item(), tmax[2].item()
+        launches = int(tsum[3].item())
+    status = lib.read_status()
+    total_flops = mlp.flops_per_step_global
+    value = total_flops / ms / 1e9
+
+    # e2e: the same step through the host-pointer entry point (pinned host inputs, H2D and D2H inside the timed region)
+    e2e = mlp.e2e(steps=min(steps, 10), warmup=2)
+    if world > 1:
+        t2 = torch.tensor([e2e["ms"]], device="cuda", dtype=torch.float64)
+        tdist.all_reduce(t2, op=tdist.ReduceOp.MAX)
+        e2e["ms"] = t2.item()
+    e2e_obj = {"value": total_flops / e2e["ms"] / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d"] * world,
+               "d2h_bytes_per_step": e2e["d2h"] * world, "ms_per_step": e2e["ms"], "api": "afb_gemm_host (C ABI, pinned host buffers)"}
+
+    if rank != 0:
+        return 0
+    # roofline of the dominant kernel (the prefill kernel of the up-projection: no exchange inside its events)
+    up_flops = gemm_flops(mlp.m, mlp.up_n_local, mlp.up_k)
+    achieved = up_flops / up_ms / 1e9
+    roofline = {"kernel": "prefill_kernel<8,false,256> (up-projection shard)", "bound": "tensor", "achieved": achieved,
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                "peak_source": f"{peaks['_source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
+                "frac_of_nominal": achieved / NOMINAL["bf16_tflops"], "avg_launch_ms": up_ms,
+                "traffic": None, "algorithmic_bytes": gemm_bytes(mlp.m, mlp.up_n_local, mlp.up_k, 8, 0)}
+    line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint8->fp32", "data": "synthetic",
+            "config": {**headline_config(world), "exchange": mlp.exchange_name}, "clocks": clocks, "e2e": e2e_obj, "gpu_launches": launches,
+            "roofline": roofline, "per_gemm_ms": {"up": up_ms, "down_incl_exchange": down_ms}, "device_status": status}
+    if world == 1:
+        cases = []
+        if not args.no_cases:
+            for name in ("decode-m1", "decode-m4", "decode-m16", "prefill", "int4-m1", "int4-m16", "int4-m128", "int4-m4096"):
+                m, n, k, bits, group = SINGLE_CASES[name]
+                cases.append(single_case(lib, torch, name, m, n, k, bits, group, peaks, 50 if m <= 128 else 10, 5))
+            line["cases"] = cases
+            d16 = next(c for c in cases if c["name"] == "decode-m16")
+            line["roofline_decode"] = {"kernel": "decode_kernel<8,2,false>", "bound": "hbm", "achieved": d16["gbs"], "peak": peaks["hbm_gbs"],
+                                       "unit": "GB/s", "frac": d16["gbs"] / peaks["hbm_gbs"], "peak_source": f"{peaks['_source']} copy bandwidth",
+                                       "traffic": None}
+        if not args.no_cpu:
+            v, info, _ = cpu_arm()
+            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="sharded-mlp", choices=["sharded-mlp"] + sorted(SINGLE_CASES))
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--no-cases", action="store_true", help="skip the single-GPU case sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -47,7 +47,7 @@ extern "C" {
 #define AFB_VARIANT_PREFILL 2u /* TMA + tcgen05/TMEM kernel                                    */
 #define AFB_VARIANT_NAIVE   3u /* one thread per output element, fp32, order of host_ref.hpp:15-24 */
 
-#define AFB_FLAG_C_F32 1u /* naive variant only: C is fp32 [M,N] instead of bf16 (exact comparison with the CPU oracle) */
+#define AFB_FLAG_C_F32 1u /* C is fp32 [M,N] instead of bf16: prefill variant (partial sums of a K-split) and naive variant */
 
 /*
  * Kernel argument block.  The first ten fields are the reference's packed kernarg
@@ -124,11 +124,38 @@ int afb_dequant_dump(const afb_gemm_args* args, void* out_bf16, void* stream);
 int afb_read_status(int32_t out[4]);
 
 /* ---- row-parallel (K-split) exchange over peer memory --------------------------- */
-/* No reference counterpart (the reference is single-GPU, bfAintBGemm.cc:63).          */
+/* No reference counterpart (the reference is single-GPU, bfAintBGemm.cc:63).  One process per GPU;
+ * buffers allocated with afb_malloc are exported to the other processes of the box and mapped there. */
 #define AFB_IPC_HANDLE_BYTES 64
+#define AFB_MAX_RANKS 8
 int afb_ipc_export(void* dev_ptr, unsigned char handle[AFB_IPC_HANDLE_BYTES]);
 int afb_ipc_import(const unsigned char handle[AFB_IPC_HANDLE_BYTES], void** dev_ptr);
 int afb_ipc_release(void* dev_ptr);
+
+/* All-reduce of the K-split partial sums as ONE kernel per GPU over peer memory (plain peer
+ * loads/stores through NVLink; no multicast): rank r waits until every rank's partial is complete,
+ * sums rows block r of all `world` partials in rank order (fp32), rounds to bf16 and stores the
+ * result into every rank's C, then waits until every rank has stored its block here.  When the
+ * kernel ends on a rank, that rank's C holds the complete sum and no peer reads its partial any more.
+ * Pointer arrays are indexed by rank and hold addresses valid in THIS process (own buffers: the
+ * local pointer; peers': afb_ipc_import).  `signals[r]` is rank r's uint32[2 * AFB_MAX_RANKS] array,
+ * zero before first use.  `epoch` must increase by one per call, identically on all ranks, from 1.
+ * Every wait is bounded; on expiry the kernel returns and afb_read_status reports AFB_ERR_TIMEOUT. */
+typedef struct afb_allreduce_args {
+    void*     partial[AFB_MAX_RANKS]; /* [M,N] ld = ld_partial; fp32 (partial_f32 = 1) or bf16 */
+    void*     c[AFB_MAX_RANKS];       /* bf16 [M,N], ldc */
+    uint32_t* signals[AFB_MAX_RANKS];
+    uint32_t  rank, world;
+    uint32_t  m, n, ld_partial, ldc;
+    uint32_t  partial_f32;
+    uint32_t  epoch;
+    uint32_t  wait_ms;                /* bound of each wait in milliseconds (0 = 2000) */
+    uint32_t  reserved;
+} afb_allreduce_args;
+int afb_ksplit_allreduce_launch(const afb_allreduce_args* args, void* stream);
+/* fp32 [rows, cols] (ld_src) -> bf16 (ld_dst), round to nearest even: finishes a K-split whose partial
+ * sums were combined by a library collective instead of afb_ksplit_allreduce_launch. */
+int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uint32_t cols, uint32_t ld_dst, uint32_t ld_src, void* stream);
 
 /* ---- diagnostics ------------------------------------------------------------- */
 const char* afb_status_string(int status);

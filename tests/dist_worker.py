@@ -1,0 +1,132 @@
+"""Rank program of the multi-process tests (launched by torch.distributed.run).
+
+mode cpu: gloo ranks on CPU.  Every rank computes its shard of the column-parallel and row-parallel GEMMs
+          with the CPU oracle, using the partition functions of awesome_fusion_b200.dist; shards are combined
+          with gloo collectives and compared with the unsplit oracle.  No GPU, no CUDA library calls.
+mode gpu: nccl ranks, one per GPU.  The same check with the CUDA kernels: N-split shards must concatenate to the
+          single-GPU result bit for bit, and the K-split exchange (fused peer-memory kernel and the NCCL path)
+          must match the oracle within tolerance, bit-identically on every rank, over several steps.
+Prints "DIST-OK <mode>" on rank 0 when everything held.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as tdist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+import afb_testlib as T  # noqa: E402
+from awesome_fusion_b200 import dist as D  # noqa: E402
+
+
+def sub_case(case, n_rng=None, k_rng=None):
+    d = dict(case.__dict__)
+    if n_rng:
+        lo, hi = n_rng
+        d.update(n=hi - lo, b=np.ascontiguousarray(case.b[lo:hi]), scale=np.ascontiguousarray(case.scale[lo:hi]), q=case.q[lo:hi])
+    if k_rng:
+        lo, hi = k_rng
+        d.update(k=hi - lo, a=np.ascontiguousarray(case.a[:, lo:hi]), b=np.ascontiguousarray(case.b[:, lo:hi]), q=case.q[:, lo:hi], ldb=hi - lo)
+    return T.Case(**d)
+
+
+def main():
+    mode = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    oracle = T.load_oracle()
+    case = T.make_case(96, 512, 1024, seed=21)            # identical on every rank (same seed)
+    ref = oracle.gemm(case, threads=2)
+    if mode == "cpu":
+        tdist.init_process_group("gloo")
+        # column-parallel: shards concatenate exactly
+        n_lo, n_hi = D.column_shard(case.n, world, rank)
+        part = torch.from_numpy(oracle.gemm(sub_case(case, n_rng=(n_lo, n_hi))))
+        sizes = [D.column_shard(case.n, world, r) for r in range(world)]
+        assert sizes[0][0] == 0 and sizes[-1][1] == case.n and all(sizes[i][1] == sizes[i + 1][0] for i in range(world - 1))
+        parts = [torch.empty((case.m, hi - lo)) for lo, hi in sizes]
+        tdist.all_gather(parts, part)
+        assert np.array_equal(torch.cat(parts, dim=1).numpy().view(np.uint32), ref.view(np.uint32)), "N-split concat != unsplit"
+        # row-parallel: partial sums add up to the unsplit result (fp32 order differs: tolerance, not bits)
+        k_lo, k_hi = D.k_shard(case.k, world, rank)
+        ks = [D.k_shard(case.k, world, r) for r in range(world)]
+        assert ks[0][0] == 0 and ks[-1][1] == case.k and all((hi - lo) % 64 == 0 for lo, hi in ks)
+        partial = torch.from_numpy(oracle.gemm(sub_case(case, k_rng=(k_lo, k_hi))))
+        tdist.all_reduce(partial)
+        err = np.abs(partial.numpy() - ref).max() / T.rms(ref)
+        assert err < 1e-5, err
+        # ragged splits keep whole units
+        assert D.split_range(28672, 8, 3, 64) == (3 * 3584, 4 * 3584)
+        assert [D.split_range(640, 3, r, 64) for r in range(3)] == [(0, 256), (256, 448), (448, 640)]
+        tdist.barrier()
+        if rank == 0:
+            print("DIST-OK cpu")
+        return
+
+    # ---- gpu ----
+    import awesome_fusion_b200 as pkg
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    tdist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = pkg.load(); lib.init(local)
+    stream = torch.cuda.current_stream().cuda_stream
+    m, n, k = 256, 1024, 4096
+    case = T.make_case(m, n, k, seed=33)
+    ref = oracle.gemm(case, threads=4)
+    # column-parallel shards vs the single-GPU run of the same kernels
+    whole, _ = T.run_case(lib, case)
+    n_lo, n_hi = D.column_shard(n, world, rank)
+    mine, _ = T.run_case(lib, sub_case(case, n_rng=(n_lo, n_hi)))
+    assert np.array_equal(mine, whole[:, n_lo:n_hi]), "column shard differs from the unsplit run"
+    # row-parallel: fused and NCCL exchanges
+    k_lo, k_hi = D.k_shard(k, world, rank)
+    shard = sub_case(case, k_rng=(k_lo, k_hi))
+    d_a, d_b, d_s = lib.to_device(shard.a), lib.to_device(shard.b), lib.to_device(shard.scale)
+    for partial in ("f32", "bf16"):
+        px = D.PeerExchange(lib, tdist, rank, world, m, n, partial_f32=(partial == "f32"))
+        assert px.ok, getattr(px, "error", "peer exchange setup failed")
+        args = lib.make_args(px.partial, d_a, d_b, d_s, m, n, shard.k, flags=pkg.FLAG_C_F32 if partial == "f32" else 0)
+        outs = []
+        for step in range(3):
+            lib.memset(px.c, 0, m * n * 2)
+            tdist.barrier(); torch.cuda.synchronize()
+            lib.gemm_launch(args, stream)
+            px.allreduce(stream)
+            torch.cuda.synchronize()
+            outs.append(lib.to_host(px.c, (m, n), np.uint16))
+        st = lib.read_status()
+        assert st[0] == 0, f"device status {st}"
+        assert all(np.array_equal(outs[0], o) for o in outs[1:]), "fused exchange is not repeatable"
+        mx, nrms, _ = oracle.compare(ref, outs[0], T.rms(ref) * 0.05)
+        assert mx <= 1e-2, f"fused {partial}: max rel err {mx}"
+        # every rank holds the same bits
+        t = torch.from_numpy(outs[0].astype(np.int32)).cuda()
+        lo, hi = t.clone(), t.clone()
+        tdist.all_reduce(lo, op=tdist.ReduceOp.MIN); tdist.all_reduce(hi, op=tdist.ReduceOp.MAX)
+        assert torch.equal(lo, hi), "ranks disagree on the all-reduced result"
+        if rank == 0:
+            print(f"fused {partial}: max rel err {mx:.3e} nrms {nrms:.3e}", flush=True)
+        px.close()
+    # NCCL comparison path
+    p32 = torch.empty((m, n), device="cuda", dtype=torch.float32)
+    c16 = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    args = lib.make_args(p32, d_a, d_b, d_s, m, n, shard.k, flags=pkg.FLAG_C_F32)
+    lib.gemm_launch(args, stream)
+    tdist.all_reduce(p32)
+    D.cast_f32_to_bf16(lib, c16.data_ptr(), p32.data_ptr(), m, n, stream)
+    torch.cuda.synchronize()
+    got = c16.view(torch.int16).cpu().numpy().view(np.uint16)
+    mx, _, _ = oracle.compare(ref, got, T.rms(ref) * 0.05)
+    assert mx <= 1e-2, f"nccl path: {mx}"
+    for p in (d_a, d_b, d_s):
+        lib.free(p)
+    tdist.barrier()
+    if rank == 0:
+        print("DIST-OK gpu")
+    tdist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,49 @@
+"""Multi-process tests of the sharded path.  CPU: two gloo ranks exercise the partition arithmetic against the
+oracle.  GPU (needs >= 2 GPUs in the box): two nccl ranks run the CUDA kernels and the peer-memory exchange."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
+def _launch(mode, world, timeout):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), mode]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
+    return subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout, env=env)
+
+
+def test_partition_functions():
+    from awesome_fusion_b200 import dist as D
+    for total, world, mult in [(28672, 8, 64), (8192, 8, 8), (4096, 3, 64), (1024, 1, 128)]:
+        rngs = [D.split_range(total, world, r, mult) for r in range(world)]
+        assert rngs[0][0] == 0 and rngs[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(rngs, rngs[1:]))
+        assert all((hi - lo) % mult == 0 for lo, hi in rngs)
+        assert max(hi - lo for lo, hi in rngs) - min(hi - lo for lo, hi in rngs) <= mult
+    with pytest.raises(ValueError):
+        D.split_range(100, 4, 0, 64)
+    assert D.k_shard(8192, 2, 1, bits=4, group=128) == (4096, 8192)
+
+
+def test_sharding_on_two_cpu_ranks():
+    res = _launch("cpu", 2, 300)
+    assert res.returncode == 0 and "DIST-OK cpu" in res.stdout, res.stdout[-3000:]
+
+
+@pytest.mark.gpu
+def test_sharding_on_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in the box")
+    res = _launch("gpu", 2, 600)
+    assert res.returncode == 0 and "DIST-OK gpu" in res.stdout, res.stdout[-4000:]
