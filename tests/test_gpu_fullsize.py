@@ -56,7 +56,11 @@ def test_int4_group_config(afb, oracle, m):
     got, _ = T.run_case(afb, case)
     rows = list(range(min(m, 2)))
     ref = oracle.gemm(case, threads=8, rows=rows)
-    check_close(oracle, ref, got[rows], f"int4 g128 M={m}", floor_frac=1.0 if m > 16 else 0.05)
+    if m > 16:   # prefill variant: weights are bf16_rn(q * s) (see test_prefill_int4_and_groups)
+        check_close(oracle, ref, got[rows], f"int4 g128 M={m}", tol=1.5e-2, floor_frac=1.0)
+        check_close(oracle, oracle.gemm(case, threads=8, rows=rows, round_w=True), got[rows], f"int4 g128 M={m} (rounded-weight oracle)")
+    else:
+        check_close(oracle, ref, got[rows], f"int4 g128 M={m}")
 
 
 def test_column_split_concatenates_exactly(afb):
