@@ -24,7 +24,7 @@ EXPORTS = [
     "afb_free_host", "afb_memcpy_h2d", "afb_memcpy_d2h", "afb_memcpy_d2d", "afb_memset", "afb_event_create",
     "afb_event_record", "afb_event_sync", "afb_event_elapsed_ms", "afb_event_destroy", "afb_stream_create",
     "afb_stream_sync", "afb_stream_destroy", "afb_device_sync", "afb_gemm_launch", "afb_gemm_resolve_variant",
-    "afb_gemm_host", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
+    "afb_gemm_host", "afb_gemm_launch_static", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
     "afb_ksplit_allreduce_launch", "afb_cast_f32_to_bf16",
     "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
 ]
@@ -96,6 +96,7 @@ class Library:
         L.afb_gemm_launch.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_gemm_resolve_variant.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(ctypes.c_uint32)]
         L.afb_gemm_host.argtypes = [ctypes.POINTER(GemmArgs), vp]
+        L.afb_gemm_launch_static.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_dequant_dump.argtypes = [ctypes.POINTER(GemmArgs), vp, vp]
         L.afb_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
         L.afb_ipc_export.argtypes = [vp, ctypes.c_char_p]
@@ -231,6 +232,10 @@ class Library:
 
     def gemm_launch(self, args, stream=None):
         self.check(self.lib.afb_gemm_launch(ctypes.byref(args), stream), "afb_gemm_launch")
+
+    def gemm_launch_static_status(self, args, stream=None):
+        """afb_gemm_launch_static: the decode GEMM with library-resident scratch (allocates nothing, needs no init)."""
+        return self.lib.afb_gemm_launch_static(ctypes.byref(args), stream)
 
     def gemm_host(self, args, stream=None):
         self.check(self.lib.afb_gemm_host(ctypes.byref(args), stream), "afb_gemm_host")

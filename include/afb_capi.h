@@ -113,6 +113,14 @@ int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
  * as one call on HOST pointers: copies A, B, scale to library-owned device staging,
  * launches, copies C back, and returns when C is in host memory.                     */
 int afb_gemm_host(const afb_gemm_args* host_args, void* stream);
+/* No counterpart in the reference.  The decode GEMM (M <= 16, B in [N,K] layout) for callers that must not
+ * allocate: programs whose framework already owns all device memory, and latency-critical loops that cannot
+ * afford the device-wide synchronisation of cudaMalloc.  Needs no afb_init and calls no allocator: its split-K
+ * scratch is a fixed array inside the library (about 4 MiB held on every GPU that loads libafb.so).
+ * Limits: M * N <= 524288 and N <= 524288, else AFB_ERR_TOO_LARGE.  All calls on a device share the array:
+ * calls that overlap on the GPU race, so keep them on one stream.  The first call on each device does a
+ * one-time set-up (address look-up and a clearing memset on `stream`): make it before any stream capture. */
+int afb_gemm_launch_static(const afb_gemm_args* args, void* stream);
 /* Dequantised weights exactly as the kernels feed them to the tensor cores:
  * out is bf16 with B's logical shape and layout ([N,K] ld=K for COL, [K,N] ld=N for ROW).
  * group_size == 0: the exact integer value; else bf16_rn(float(q) * float(scale)).
