@@ -1,23 +1,26 @@
 // Decode variant (M <= 16, B in [N,K] layout): the memory-bound replacement of the
 // reference kernel's main loop (bf16gemm_kernel_gfx90a.s:410-489) for GEMV-like shapes.
 //
-// Every weight byte is read from HBM exactly once with 128-bit loads; the dominant
-// stream is B (N*K*bits/8 bytes).  A CTA owns 128 output channels (16 per warp) and one
-// K-slice.  Per 16-byte load a lane holds 16 (int8) or 32 (int4) consecutive-k weights of
-// one channel; they are unpacked to exact bf16 in registers (dequant.cuh) and fed to
-// mma.sync.m16n8k16 as the 16-row operand, the <= 16 activation rows being the 8-column
-// operand.  The four lanes of a quad hold different k, so the tensor-core instruction
-// performs the intra-warp split-K reduction; slices of K owned by different CTAs are
-// combined through an fp32 workspace by the last CTA to arrive (fixed summation order,
-// so results are run-to-run identical).
+// Every weight byte is read from HBM exactly once; the dominant stream is B (N*K*bits/8 bytes).
+// A CTA has 8 warps arranged WR x WK: it owns 16*WR output channels and one K-slice, and the WK warps
+// that share 16 channels take interleaved 64-byte chunks of K.  Each warp streams its chunks through a
+// private ring in shared memory with 16-byte cp.async copies (deep memory-level parallelism without
+// holding registers; the ring keeps filling across the block-wide barriers); a lane then reads back its own 16 bytes =
+// 16 (int8) or 32 (int4) consecutive-k weights of one channel, unpacks them to exact bf16 in registers
+// (dequant.cuh) and feeds mma.sync.m16n8k16 with the 16 channels as the row operand and the <= 16
+// activation rows as the column operand.  The four lanes of a quad hold different k, so the tensor-core
+// instruction performs the intra-warp split-K reduction; the WK warps are reduced through shared memory,
+// and K-slices owned by different CTAs are combined through an fp32 workspace by the last CTA to arrive
+// (fixed summation order, so results are run-to-run identical).
 //
-// Because a dot product does not care about the order of k, weights are paired in the
-// order that is cheapest to unpack ({k0,k2},{k1,k3} for int8; {k0,k4}..{k3,k7} for int4)
-// and the activations are permuted to match once, while they are staged in shared memory.
+// Because a dot product does not care about the order of k, weights are paired in the order that is
+// cheapest to unpack ({k0,k2},{k1,k3} for int8; {k0,k4}..{k3,k7} for int4); the activations of the CTA's
+// K range are staged once per pass in shared memory, already permuted to match, and shared by all warps.
 //
-// Scales: per-channel scales multiply the fp32 sum once at the end (the reference
-// multiplies every weight, .s:29-33; mathematically the same, one rounding fewer).
-// Per-group scales multiply the fp32 partial sum of each group.
+// Scales: per-channel scales multiply the fp32 sum once at the end (the reference multiplies every
+// weight, .s:29-33; mathematically the same, one rounding fewer).  Per-group scales multiply the fp32
+// partial sum of each chunk (a chunk never straddles a group).
+#include <cstdlib>
 #include "afb_internal.h"
 #include "dequant.cuh"
 
@@ -26,10 +29,15 @@ namespace afb {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kRowsPerCta = 128;
-constexpr int kStageK = 1024;                 // activations staged per pass (k elements)
-constexpr int kActRowBytes = kStageK * 2 + 16;  // +16: rows land in different bank groups
-constexpr int kMaxGroupsPerStage = 8;         // group_size >= 128
+constexpr int kWarps = 8;
+constexpr int kRing = 4;                       // cp.async stages per warp (power of two)
+constexpr int kStageBytes = 1024;              // 2 channels x 32 lanes x 16 bytes
+constexpr int kRingBytes = kWarps * kRing * kStageBytes;   // 32 KiB
+constexpr int kRedFloats = kWarps * 16 * 17;   // cross-warp reduction buffer, [warp][16 channels][<=16 rows + pad]
+constexpr int kActBytes = 32 * 1024;           // staged activations of one pass: m rows x (pass_k * 2 + 16) bytes
+constexpr int kOffRed = kRingBytes;
+constexpr int kOffAct = kOffRed + kRedFloats * 4 + 16;
+constexpr int kSmemBytes = kOffAct + kActBytes;   // 73.5 KiB: three CTAs per SM
 
 struct DecodeParams {
     const uint16_t* a;
@@ -38,16 +46,29 @@ struct DecodeParams {
     uint16_t* c;
     uint32_t m, n, k, lda, ldb_bytes, ldc;
     uint32_t enc, scale_dtype, group;
+    uint32_t wr;      // warps along the channel dimension (1, 2, 4 or 8); WK = 8 / wr
     uint32_t kc;      // k elements per slice (multiple of the chunk)
+    uint32_t pass_k;  // k elements staged per pass (multiple of chunk * WK; m * (pass_k * 2 + 16) <= kActBytes)
+    uint32_t group_shift;  // log2(group) (groups are powers of two)
     uint32_t slices;  // gridDim.y
     float* ws;        // [slices][m][n] fp32 partial sums (slices > 1)
-    uint32_t* counters;  // one per row block, zero on entry, zero again on exit
+    uint32_t* counters;  // one per CTA column, zero on entry, zero again on exit
 };
 
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_act(const uint16_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -56,186 +77,211 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t swz_piece(uint32_t pc) { return pc ^ (((pc >> 3) & 1u) << 1); }
 __device__ __forceinline__ float bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+__device__ __forceinline__ float load_scale(const void* s, size_t idx, uint32_t dtype) {
+    return dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(s)[idx]) : reinterpret_cast<const float*>(s)[idx];
+}
+
+__device__ __forceinline__ uint32_t swz_piece(uint32_t pc) { return pc ^ (((pc >> 3) & 1u) << 1); }
 
 template <int BITS, int MT, bool GROUPED>
-__global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(const DecodeParams p) {
-    constexpr int CH = BITS == 8 ? 64 : 128;    // k per warp chunk (a quad covers 64 bytes of one row)
+__global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams p) {
+    constexpr int CH = BITS == 8 ? 64 : 128;    // k per chunk (a quad covers 64 bytes of one channel)
     constexpr int LK = CH / 4;                  // k per lane per chunk
-    constexpr int PIECES = LK / 8;              // 16-byte activation pieces per lane per chunk
-    constexpr int U = 4;                        // chunks in flight per warp
+    constexpr int AV = LK / 8;                  // 16-byte activation vectors per lane, row and chunk
 
-    __shared__ __align__(16) uint8_t s_act[MT * 8 * kActRowBytes];
-    __shared__ float s_scale[GROUPED ? kRowsPerCta * kMaxGroupsPerStage : 1];
-    __shared__ uint32_t s_last;
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* s_red = reinterpret_cast<float*>(smem + kOffRed);
+    uint32_t* s_last = reinterpret_cast<uint32_t*>(smem + kOffRed + kRedFloats * 4);
+    const uint32_t s_act = (uint32_t)__cvta_generic_to_shared(smem + kOffAct);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
-    const uint32_t nblk = blockIdx.x * kRowsPerCta;
-    const uint32_t row_a = nblk + warp * 16 + g, row_b = row_a + 8;
+    const uint32_t wk_count = kWarps / p.wr;
+    const uint32_t wr = warp / wk_count, wk = warp % wk_count;
+    const uint32_t nblk = blockIdx.x * 16 * p.wr;
+    const uint32_t row_a = nblk + wr * 16 + g, row_b = row_a + 8;
     const bool ok_a = row_a < p.n, ok_b = row_b < p.n;
     const uint8_t* pa = p.b + (size_t)(ok_a ? row_a : 0) * p.ldb_bytes + tig * 16;
     const uint8_t* pb = p.b + (size_t)(ok_b ? row_b : 0) * p.ldb_bytes + tig * 16;
     const uint32_t ks = blockIdx.y * p.kc;
     const uint32_t kend = min(p.k, ks + p.kc);
+    const uint32_t nchunks = (kend - ks) / CH;
+    const uint32_t my_chunks = nchunks > wk ? (nchunks - wk + wk_count - 1) / wk_count : 0;
+    const size_t kbyte0 = BITS == 8 ? ks : (ks >> 1);
     const uint32_t xormask = (BITS == 8 && p.enc == AFB_ENC_OFFSET_BINARY) ? 0x80808080u : 0u;
     const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
-    const uint32_t groups_per_row = GROUPED ? p.k / p.group : 0;
+    const uint32_t groups_per_row = GROUPED ? (p.k >> p.group_shift) : 0;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * (kRing * kStageBytes) + lane * 16;
+    const uint32_t act_row_bytes = p.pass_k * 2 + 16;   // +16: consecutive rows land in different bank groups
+
+    // Shared-memory address of this lane's staged activations.  Rows beyond m are never staged: such a lane reads
+    // row 0 instead, which only feeds output columns (activation rows) that are never stored.
+    uint32_t act_base[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) act_base[mt] = s_act + ((uint32_t)(mt * 8 + g) < p.m ? mt * 8 + g : 0) * act_row_bytes;
+    // piece (16-byte) offsets inside a chunk after the bank swizzle: bit 3 of the piece index flips bit 1.
+    // int4: 16 pieces per chunk, so bit 3 depends on the lane only; int8: 8 pieces per chunk, bit 3 = chunk parity.
+    uint32_t act_off[AV];
+#pragma unroll
+    for (int v = 0; v < AV; ++v) act_off[v] = (BITS == 4 ? swz_piece(tig * AV + v) : (uint32_t)(tig * AV + v)) * 16;
 
     float acc[MT][4];
-    float accg[MT][4];  // partial sum of the current scale group (grouped mode only)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { acc[mt][e] = 0.f; accg[mt][e] = 0.f; }
+        for (int e = 0; e < 4; ++e) acc[mt][e] = 0.f;
 
-    for (uint32_t kb = ks; kb < kend; kb += kStageK) {
-        const uint32_t klen = min((uint32_t)kStageK, kend - kb);
-        const uint32_t nchunks = klen / CH;
-        const size_t kbyte0 = BITS == 8 ? kb : (kb >> 1);
-        // the first weight loads of this pass go out before the activations are staged
-        uint4 wa[U], wb[U];
+    // global addresses of the next chunk to copy (this warp's chunks are wk, wk + WK, ...)
+    const uint8_t* src_a = pa + kbyte0 + (size_t)wk * 64;
+    const uint8_t* src_b = pb + kbyte0 + (size_t)wk * 64;
+    const uint32_t src_step = wk_count * 64;
+    uint32_t issued = 0;
+    auto issue = [&]() {   // start the copy of this warp's next chunk into ring slot issued % kRing
+        const uint32_t dst = ring + (issued & (kRing - 1)) * kStageBytes;
+        if (ok_a) cp_async16(dst, src_a);
+        if (ok_b) cp_async16(dst + 512, src_b);
+        src_a += src_step; src_b += src_step; ++issued;
+    };
+    const uint16_t* sc_h = reinterpret_cast<const uint16_t*>(p.scale);
+    const float* sc_f = reinterpret_cast<const float*>(p.scale);
+    const size_t sc_ia = (size_t)(ok_a ? row_a : 0) * groups_per_row, sc_ib = (size_t)(ok_b ? row_b : 0) * groups_per_row;
+    uint32_t sc_k = ks + wk * CH;            // k of the chunk whose scales are fetched next
+    const uint32_t sc_kstep = wk_count * CH;
+    auto load_group_scales = [&](float& sa, float& sb) {
+        const uint32_t grp = sc_k >> p.group_shift;
+        if (p.scale_dtype == AFB_SCALE_BF16) { sa = bf16_to_f32(sc_h[sc_ia + grp]); sb = bf16_to_f32(sc_h[sc_ib + grp]); }
+        else { sa = sc_f[sc_ia + grp]; sb = sc_f[sc_ib + grp]; }
+        sc_k += sc_kstep;
+    };
+
+    // the weight stream starts before anything else and keeps running across the passes below
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            wa[u] = make_uint4(0, 0, 0, 0); wb[u] = wa[u];
-            if ((uint32_t)u < nchunks) {
-                if (ok_a) wa[u] = ldg_stream(pa + kbyte0 + (size_t)u * 64);
-                if (ok_b) wb[u] = ldg_stream(pb + kbyte0 + (size_t)u * 64);
-            }
-        }
-        __syncthreads();  // the previous pass has been consumed
-        // ---- stage (and permute) the activations of [kb, kb+klen) ----
-        const uint32_t pieces = klen >> 3;
-        for (uint32_t idx = tid; idx < (uint32_t)(MT * 8) * pieces; idx += kThreads) {
-            const uint32_t r = idx / pieces, pc = idx - r * pieces;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < p.m) v = *reinterpret_cast<const uint4*>(p.a + (size_t)r * p.lda + kb + pc * 8);
-            uint4 o;
-            if (BITS == 8) {  // {k0,k2},{k1,k3},{k4,k6},{k5,k7}
-                o.x = prmt(v.x, v.y, 0x5410u); o.y = prmt(v.x, v.y, 0x7632u);
-                o.z = prmt(v.z, v.w, 0x5410u); o.w = prmt(v.z, v.w, 0x7632u);
-            } else {          // {k0,k4},{k1,k5},{k2,k6},{k3,k7}
-                o.x = prmt(v.x, v.z, 0x5410u); o.y = prmt(v.x, v.z, 0x7632u);
-                o.z = prmt(v.y, v.w, 0x5410u); o.w = prmt(v.y, v.w, 0x7632u);
-            }
-            *reinterpret_cast<uint4*>(s_act + r * kActRowBytes + swz_piece(pc) * 16) = o;
-        }
-        if (GROUPED) {
-            const uint32_t ng = klen / p.group;  // <= kMaxGroupsPerStage
-            for (uint32_t idx = tid; idx < kRowsPerCta * ng; idx += kThreads) {
-                const uint32_t r = idx / ng, gi = idx - r * ng;
-                float s = 0.f;
-                if (nblk + r < p.n) {
-                    const size_t si = (size_t)(nblk + r) * groups_per_row + kb / p.group + gi;
-                    s = p.scale_dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(p.scale)[si])
-                                                       : reinterpret_cast<const float*>(p.scale)[si];
+    for (int j = 0; j < kRing - 1; ++j) {
+        if ((uint32_t)j < my_chunks) issue();
+        cp_async_commit();
+    }
+    float sc_a = 0.f, sc_b = 0.f, sc_a_nxt = 0.f, sc_b_nxt = 0.f;
+    if (GROUPED && my_chunks) load_group_scales(sc_a, sc_b);
+
+    uint32_t i = 0;   // chunks this warp has consumed
+    for (uint32_t pk = ks; pk < kend; pk += p.pass_k) {
+        const uint32_t plen = min(p.pass_k, kend - pk);
+        if (pk != ks) __syncthreads();   // the previous pass has been consumed by every warp
+        {   // stage the activations of [pk, pk + plen), permuted into the pairing the weights unpack to
+            const uint32_t pieces = plen >> 3;
+            for (uint32_t r = tid >> 6; r < p.m; r += 4)
+                for (uint32_t pc = tid & 63; pc < pieces; pc += 64) {
+                    const uint4 v = ldg_act(p.a + (size_t)r * p.lda + pk + pc * 8);
+                    uint4 o;
+                    if (BITS == 8) {  // {k0,k2},{k1,k3},{k4,k6},{k5,k7}
+                        o.x = prmt(v.x, v.y, 0x5410u); o.y = prmt(v.x, v.y, 0x7632u);
+                        o.z = prmt(v.z, v.w, 0x5410u); o.w = prmt(v.z, v.w, 0x7632u);
+                    } else {          // {k0,k4},{k1,k5},{k2,k6},{k3,k7}
+                        o.x = prmt(v.x, v.z, 0x5410u); o.y = prmt(v.x, v.z, 0x7632u);
+                        o.z = prmt(v.y, v.w, 0x5410u); o.w = prmt(v.y, v.w, 0x7632u);
+                    }
+                    *reinterpret_cast<uint4*>(smem + kOffAct + r * act_row_bytes + swz_piece(pc) * 16) = o;
                 }
-                s_scale[r * kMaxGroupsPerStage + gi] = s;
-            }
         }
         __syncthreads();
 
-        for (uint32_t c0 = 0; c0 < nchunks; c0 += U) {
+        const uint32_t chunks_in_pass = plen / CH;
+        uint32_t chunk_off = wk * (CH * 2);                 // byte offset of the chunk inside a staged row
+        for (uint32_t cl = wk; cl < chunks_in_pass; cl += wk_count, ++i, chunk_off += wk_count * (CH * 2)) {
+            if (issued < my_chunks) issue();
+            cp_async_commit();
+            if (GROUPED && i + 1 < my_chunks) load_group_scales(sc_a_nxt, sc_b_nxt);
+            // this lane's activations of the chunk: rows g (and g + 8), k = cl*CH + tig*LK ..
+            const uint32_t par = BITS == 8 ? ((cl & 1u) << 5) : 0u;   // int8: odd chunks have bit 3 of the piece index set
+            uint32_t s[MT][AV * 4];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (c0 + u < nchunks) {
-                    const uint32_t kk = c0 + u;
-                    const uint32_t pc0 = kk * (CH / 8) + tig * PIECES;
-                    uint32_t s[MT][PIECES * 4];
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int v = 0; v < AV; ++v) {
+                    const uint4 t = lds128(act_base[mt] + chunk_off + (act_off[v] ^ par));
+                    s[mt][4 * v] = t.x; s[mt][4 * v + 1] = t.y; s[mt][4 * v + 2] = t.z; s[mt][4 * v + 3] = t.w;
+                }
+            cp_async_wait<kRing - 1>();   // this warp's chunk i has landed (each lane reads only what it copied itself)
+            const uint32_t slot = ring + (i & (kRing - 1)) * kStageBytes;
+            const uint4 wa4 = lds128(slot), wb4 = lds128(slot + 512);
+            const uint32_t wav[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
+            const uint32_t wbv[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
+            float part[MT][4];   // grouped: the sum of this chunk alone (a chunk lies inside one scale group)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) part[mt][e] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (BITS == 8) {
+                    uint32_t a0, a1, a2, a3;
+                    s8x4_to_bf16_strided(wav[j] ^ xormask, a0, a2);
+                    s8x4_to_bf16_strided(wbv[j] ^ xormask, a1, a3);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
+                        mma_bf16(GROUPED ? part[mt] : acc[mt], a0, a1, a2, a3, s[mt][2 * j], s[mt][2 * j + 1]);
+                } else {
+                    uint32_t qa[4], qb[4];
+                    s4x8_to_bf16_strided(wav[j], magic4, qa);
+                    s4x8_to_bf16_strided(wbv[j], magic4, qb);
 #pragma unroll
-                        for (int i = 0; i < PIECES; ++i) {
-                            const uint4 t = *reinterpret_cast<const uint4*>(s_act + (mt * 8 + g) * kActRowBytes + swz_piece(pc0 + i) * 16);
-                            s[mt][4 * i] = t.x; s[mt][4 * i + 1] = t.y; s[mt][4 * i + 2] = t.z; s[mt][4 * i + 3] = t.w;
-                        }
-                    const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
-                    const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
-                    // the registers just read are refilled with the chunk U steps ahead
-                    if (kk + U < nchunks) {
-                        if (ok_a) wa[u] = ldg_stream(pa + kbyte0 + (size_t)(kk + U) * 64);
-                        if (ok_b) wb[u] = ldg_stream(pb + kbyte0 + (size_t)(kk + U) * 64);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (BITS == 8) {
-                            uint32_t a0, a1, a2, a3;
-                            s8x4_to_bf16_strided(wav[j] ^ xormask, a0, a2);
-                            s8x4_to_bf16_strided(wbv[j] ^ xormask, a1, a3);
-#pragma unroll
-                            for (int mt = 0; mt < MT; ++mt)
-                                mma_bf16(GROUPED ? accg[mt] : acc[mt], a0, a1, a2, a3, s[mt][2 * j], s[mt][2 * j + 1]);
-                        } else {
-                            uint32_t qa[4], qb[4];
-                            s4x8_to_bf16_strided(wav[j], magic4, qa);
-                            s4x8_to_bf16_strided(wbv[j], magic4, qb);
-#pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) {
-                                mma_bf16(GROUPED ? accg[mt] : acc[mt], qa[0], qb[0], qa[1], qb[1], s[mt][4 * j], s[mt][4 * j + 1]);
-                                mma_bf16(GROUPED ? accg[mt] : acc[mt], qa[2], qb[2], qa[3], qb[3], s[mt][4 * j + 2], s[mt][4 * j + 3]);
-                            }
-                        }
-                    }
-                    if (GROUPED) {
-                        const uint32_t kdone = (kk + 1) * CH;  // k consumed in this pass
-                        if (kdone % p.group == 0) {
-                            const uint32_t gi = kdone / p.group - 1;
-                            const float sa = s_scale[(warp * 16 + g) * kMaxGroupsPerStage + gi];
-                            const float sb = s_scale[(warp * 16 + g + 8) * kMaxGroupsPerStage + gi];
-#pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) {
-                                acc[mt][0] = fmaf(sa, accg[mt][0], acc[mt][0]); acc[mt][1] = fmaf(sa, accg[mt][1], acc[mt][1]);
-                                acc[mt][2] = fmaf(sb, accg[mt][2], acc[mt][2]); acc[mt][3] = fmaf(sb, accg[mt][3], acc[mt][3]);
-                                accg[mt][0] = accg[mt][1] = accg[mt][2] = accg[mt][3] = 0.f;
-                            }
-                        }
+                    for (int mt = 0; mt < MT; ++mt) {
+                        mma_bf16(GROUPED ? part[mt] : acc[mt], qa[0], qb[0], qa[1], qb[1], s[mt][4 * j], s[mt][4 * j + 1]);
+                        mma_bf16(GROUPED ? part[mt] : acc[mt], qa[2], qb[2], qa[3], qb[3], s[mt][4 * j + 2], s[mt][4 * j + 3]);
                     }
                 }
             }
-        }
-    }
-
-    // ---- epilogue: acc[mt][e]: channel = e < 2 ? row_a : row_b, activation row = mt*8 + 2*tig + (e & 1)
-    if (p.slices == 1) {
-        float sa = 1.f, sb = 1.f;
-        if (!GROUPED) {
-            if (ok_a) sa = p.scale_dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(p.scale)[row_a])
-                                                          : reinterpret_cast<const float*>(p.scale)[row_a];
-            if (ok_b) sb = p.scale_dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(p.scale)[row_b])
-                                                          : reinterpret_cast<const float*>(p.scale)[row_b];
-        }
+            if (GROUPED) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t mm = mt * 8 + 2 * tig + (e & 1);
-                const uint32_t nn = e < 2 ? row_a : row_b;
-                if (mm < p.m && nn < p.n)
-                    p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[mt][e] * (e < 2 ? sa : sb)));
+                for (int mt = 0; mt < MT; ++mt) {
+                    acc[mt][0] = fmaf(sc_a, part[mt][0], acc[mt][0]); acc[mt][1] = fmaf(sc_a, part[mt][1], acc[mt][1]);
+                    acc[mt][2] = fmaf(sc_b, part[mt][2], acc[mt][2]); acc[mt][3] = fmaf(sc_b, part[mt][3], acc[mt][3]);
+                }
+                sc_a = sc_a_nxt; sc_b = sc_b_nxt;
             }
-        return;
+        }
     }
 
-    // several K-slices: publish this slice's partial sums, the last CTA of the row block adds them up
+    // ---- reduce the WK warps that share 16 channels.  acc[mt][e]: channel = e < 2 ? g : g + 8, activation row = mt*8 + 2*tig + (e & 1)
+    constexpr int MCOLS = 8 * MT;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const uint32_t mm = mt * 8 + 2 * tig + (e & 1);
-            const uint32_t nn = e < 2 ? row_a : row_b;
-            if (mm < p.m && nn < p.n) __stcg(p.ws + ((size_t)blockIdx.y * p.m + mm) * p.n + nn, acc[mt][e]);
+        for (int e = 0; e < 4; ++e)
+            s_red[(warp * 16 + (e < 2 ? g : g + 8)) * 17 + mt * 8 + 2 * tig + (e & 1)] = acc[mt][e];
+    __syncthreads();
+
+    const uint32_t rows_cta = 16 * p.wr;
+    const uint32_t outputs = rows_cta * MCOLS;          // <= 2048
+    const bool single = p.slices == 1;
+    for (uint32_t idx = tid; idx < outputs; idx += kThreads) {
+        const uint32_t mm = idx / rows_cta, r = idx - mm * rows_cta;   // consecutive threads -> consecutive channels
+        const uint32_t nn = nblk + r;
+        if (mm >= p.m || nn >= p.n) continue;
+        const uint32_t w0 = (r >> 4) * wk_count;
+        float sum = 0.f;
+        for (uint32_t w = 0; w < wk_count; ++w) sum += s_red[((w0 + w) * 16 + (r & 15)) * 17 + mm];
+        if (single) {
+            if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
+            p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
+        } else {
+            __stcg(p.ws + ((size_t)blockIdx.y * p.m + mm) * p.n + nn, sum);
         }
+    }
+    if (single) return;
+
+    // several K-slices: the last CTA of this column of CTAs adds the published partial sums in slice order
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const uint32_t old = atomicAdd(p.counters + blockIdx.x, 1u);
-        s_last = (old == p.slices - 1) ? 1u : 0u;
+        *s_last = (old == p.slices - 1) ? 1u : 0u;
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!*s_last) return;
     __threadfence();
-    for (uint32_t idx = tid; idx < p.m * kRowsPerCta; idx += kThreads) {
-        const uint32_t mm = idx / kRowsPerCta, nn = nblk + (idx % kRowsPerCta);
+    for (uint32_t idx = tid; idx < p.m * rows_cta; idx += kThreads) {
+        const uint32_t mm = idx / rows_cta, nn = nblk + (idx % rows_cta);
         if (nn >= p.n) continue;
         const float* src = p.ws + (size_t)mm * p.n + nn;
         const size_t slice_stride = (size_t)p.m * p.n;
@@ -247,9 +293,7 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
 #pragma unroll
             for (int i = 0; i < 8; ++i) sum += v[i];
         }
-        if (!GROUPED)
-            sum *= p.scale_dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(p.scale)[nn])
-                                                  : reinterpret_cast<const float*>(p.scale)[nn];
+        if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
         p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
     }
     if (tid == 0) p.counters[blockIdx.x] = 0u;  // ready for the next launch
@@ -257,7 +301,16 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
 
 template <int BITS, int MT, bool GROUPED>
 cudaError_t launch_one(const DecodeParams& p, dim3 grid, cudaStream_t s) {
-    decode_kernel<BITS, MT, GROUPED><<<grid, kThreads, 0, s>>>(p);
+    auto kern = decode_kernel<BITS, MT, GROUPED>;
+    static int attr_dev = -1;   // per template instance
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_dev = dev;
+    }
+    kern<<<grid, kThreads, kSmemBytes, s>>>(p);
     return cudaGetLastError();
 }
 
@@ -272,24 +325,47 @@ bool decode_supports(const afb_gemm_args& a) {
     const uint32_t ldb_bytes = a.b_bits == 8 ? a.ldb : a.ldb / 2;
     if (ldb_bytes % 16 || a.lda % 8) return false;
     if ((uintptr_t)a.ptr_a % 16 || (uintptr_t)a.ptr_b % 16) return false;
-    if (a.group_size) {
-        if (a.group_size % 128 || a.group_size > kStageK || kStageK % a.group_size || a.k % a.group_size) return false;
-    }
+    if (a.group_size && (a.group_size % ch || a.k % a.group_size || (a.group_size & (a.group_size - 1)))) return false;   // power of two; a chunk never straddles a group
     return true;
 }
 
-// Number of K-slices and slice length: enough CTAs to fill the GPU about three times over,
-// slices a power-of-two fraction of K (multiple of 4 chunks and of the group).
-static void pick_slices(const afb_gemm_args& a, int sm_count, size_t ws_bytes, uint32_t& slices, uint32_t& kc) {
+// Shape of the launch: warps per CTA along the channels (wr), K-slices (slices) and slice length (kc).
+//   * wr: activations are re-read by every column of CTAs, so more activation rows ask for more channels per CTA
+//     (keeps the activation traffic through L2 below about half of the weight traffic);
+//   * slices: only when the channel dimension alone cannot fill the GPU.
+static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, size_t counter_count, DecodeParams& p) {
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
-    uint32_t unit = 4 * ch;
-    if (a.group_size > unit) unit = a.group_size;
-    const uint32_t row_blocks = (a.n + kRowsPerCta - 1) / kRowsPerCta;
+    const uint32_t sms = (uint32_t)sm_count;
+    const uint32_t act_bytes_per_k = 2 * a.m;                      // per k, per column of CTAs
+    uint32_t wr = 1;
+    while (wr < 8 && act_bytes_per_k * 2 > 16 * wr * a.b_bits / 8) wr *= 2;     // activation bytes <= half the weight bytes
+    const double weight_mb = (double)a.n * a.k * a.b_bits / 8 / 1e6;
+    auto ctas = [&](uint32_t w) { return (a.n + 16 * w - 1) / (16 * w); };
+    while (wr < 8 && ctas(wr * 2) >= 6 * sms) wr *= 2;              // plenty of channels: larger CTAs, fewer activation re-reads
+    while (wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > (size_t)kActBytes) wr *= 2;   // one round of the WK warps must fit the staging area
+    const uint32_t want = weight_mb < 48.0 ? sms * 3 / 2 : sms * 5;   // many small CTAs even out the load of the SMs (measured)
     uint32_t s = 1;
-    while (row_blocks * s < 3u * (uint32_t)sm_count && s < 64 && a.k / (2 * s) >= unit && (a.k % (2 * s * unit)) == 0) s *= 2;
-    while (s > 1 && (size_t)s * a.m * a.n * sizeof(float) > ws_bytes) s /= 2;
-    slices = s;
-    kc = a.k / s;
+    const uint32_t unit = a.group_size > ch ? a.group_size : ch;
+    while (ctas(wr) * s < want && s < 32 && a.k % (2 * s * unit) == 0 && a.k / (2 * s) >= 4 * ch * (kWarps / wr)) s *= 2;
+    while (s > 1 && ((size_t)s * a.m * a.n * sizeof(float) > ws_bytes || ctas(wr) > counter_count)) s /= 2;
+    if (ctas(wr) > counter_count) s = 1;
+    if (const char* e = getenv("AFB_DECODE_WR")) {       // tuning aid: force the CTA shape when it is legal
+        const uint32_t v = (uint32_t)atoi(e);
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= (size_t)kActBytes) wr = v;
+    }
+    if (const char* e = getenv("AFB_DECODE_SLICES")) {   // tuning aid: force the number of K-slices when it is legal
+        const uint32_t v = (uint32_t)atoi(e);
+        if (v >= 1 && v <= 64 && a.k % (v * unit) == 0 && (size_t)v * a.m * a.n * sizeof(float) <= ws_bytes && ctas(wr) <= counter_count) s = v;
+    }
+    p.wr = wr; p.slices = s; p.kc = a.k / s;
+    // activations staged per pass: as many k as fit the staging area, in whole rounds of the WK warps
+    const uint32_t round = ch * (kWarps / wr);
+    uint32_t pass_max = ((uint32_t)kActBytes / a.m - 16) / 2 / round * round;   // >= 512 k for m <= 16, round <= 512
+    if (pass_max == 0) pass_max = round;
+    const uint32_t npass = (p.kc + pass_max - 1) / pass_max;
+    p.pass_k = ((p.kc + npass - 1) / npass + round - 1) / round * round;        // equal passes, whole rounds
+    p.group_shift = 0;
+    while (a.group_size && (1u << p.group_shift) < a.group_size) ++p.group_shift;
 }
 
 int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t ws_bytes, uint32_t* counters,
@@ -303,11 +379,9 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
     p.m = a.m; p.n = a.n; p.k = a.k; p.lda = a.lda; p.ldc = a.ldc;
     p.ldb_bytes = a.b_bits == 8 ? a.ldb : a.ldb / 2;
     p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
-    pick_slices(a, ctx->sm_count, ws_bytes, p.slices, p.kc);
+    pick_shape(a, ctx->sm_count, ws_bytes, counter_count, p);
     p.ws = ws; p.counters = counters;
-    const uint32_t row_blocks = (a.n + kRowsPerCta - 1) / kRowsPerCta;
-    if (p.slices > 1 && row_blocks > counter_count) { p.slices = 1; p.kc = a.k; }
-    dim3 grid(row_blocks, p.slices);
+    dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
     const bool grouped = a.group_size != 0;
     const int mt = a.m <= 8 ? 1 : 2;
     cudaError_t e;

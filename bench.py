@@ -165,14 +165,30 @@ def single_case(lib, torch, name, m, n, k, bits, group, peaks, steps, warmup):
     wbytes = n * k * bits // 8
     copies = max(1, min(24, -(-400_000_000 // wbytes)))   # >= 400 MB of distinct weights (L2 is 126 MB)
     op = Gemm(lib, torch, m, n, k, bits=bits, group=group, seed=1, copies=copies)
-    ms = time_launches(torch, lambda: op.launch(stream), steps, warmup)
     import awesome_fusion_b200 as pkg
     variant = {pkg.VARIANT_DECODE: "decode", pkg.VARIANT_PREFILL: "prefill", pkg.VARIANT_NAIVE: "naive"}[lib.resolve_variant(op.args[0])]
+    timing = "events around back-to-back launches"
+    if variant == "decode" and not os.environ.get("AFB_BENCH_NO_GRAPH"):
+        # a decode launch lasts a few microseconds, less than the host needs to issue it: one CUDA graph holds one launch per
+        # rotated weight buffer, so that the events time the device and not the launch loop
+        for _ in range(max(3, warmup)):
+            op.launch(stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            cs = torch.cuda.current_stream().cuda_stream
+            for _ in range(copies):
+                op.launch(cs)
+        ms = time_launches(torch, graph.replay, steps, warmup) / copies
+        timing = f"CUDA-graph replay, {copies} launches per graph"
+        del graph
+    else:
+        ms = time_launches(torch, lambda: op.launch(stream), steps, warmup)
     tf, gb = op.flops / ms / 1e9, op.bytes / ms / 1e6
     ai = op.flops / op.bytes
     bound = "hbm" if ai < peaks["bf16_tflops"] * 1e3 / peaks["hbm_gbs"] else "tensor"
     res = {"name": name, "variant": variant, "m": m, "n": n, "k": k, "bits": bits, "group": group, "us": round(ms * 1e3, 2),
-           "tflops": round(tf, 2), "gbs": round(gb, 1), "bound": bound, "weight_buffers_rotated": copies,
+           "tflops": round(tf, 2), "gbs": round(gb, 1), "bound": bound, "weight_buffers_rotated": copies, "timing": timing,
            "frac_of_measured": round(gb / peaks["hbm_gbs"] if bound == "hbm" else tf / peaks["bf16_tflops"], 4),
            "frac_of_nominal": round(gb / NOMINAL["hbm_gbs"] if bound == "hbm" else tf / NOMINAL["bf16_tflops"], 4)}
     del op
