@@ -38,7 +38,8 @@ int launch_naive(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);
 int launch_decode(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);
 int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t ws_bytes, uint32_t* counters,
                      size_t counter_count, cudaStream_t s);
-int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);
+int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);      // converted weights through shared memory
+int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);   // converted weights in tensor memory
 int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s);
 
 bool decode_supports(const afb_gemm_args& a);

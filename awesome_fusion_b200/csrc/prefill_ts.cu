@@ -1,0 +1,363 @@
+// Prefill variant, weights-in-tensor-memory form (M > 16, B in [N,K] layout).
+//
+// The GEMM is computed transposed, D[n, m] = sum_k W[n,k] * A[m,k]: a tile has 128 output channels as the
+// 128 TMEM lanes and BMA (256 or 128) activation rows as its columns.  That lets the DEQUANTISED WEIGHTS
+// be the tcgen05.mma operand that lives in tensor memory: the converter warps unpack the raw int8 / int4
+// tile to exact bf16 in registers (dequant.cuh) and write it straight to TMEM with tcgen05.st, so the
+// converted weights never touch shared memory, and only 128 x 64 weights are converted per 128 x BMA x 64
+// block of MMA work (reference counterpart of the whole kernel: bf16gemm_kernel_gfx90a.s:184-636).
+//
+//   warp 0      (1 lane)  TMA: activation tile [BMA x 64] bf16 (128-byte swizzle) + raw weight tile
+//                         [128 x 64] int8/int4 (64-/32-byte swizzle) into a ring of stages
+//   warps 2-9   (256 thr) converters: one channel per thread (two warps per lane quarter = the two 32-wide halves of K),
+//                         raw bytes -> bf16 pairs -> (x group scale) -> tcgen05.st into a ring of TMEM slots;
+//                         after the last K step the same warps run the epilogue: tcgen05.ld the accumulator,
+//                         multiply by the per-channel scale (one scalar per thread), round to bf16, store C
+//   warp 1      (1 lane)  tcgen05.mma kind::f16, A from TMEM, B (activations) from shared memory,
+//                         128 x BMA x 16, fp32 accumulator in TMEM
+// One accumulator (BMA columns) + 6 weight slots (32 columns each) live in the 512 TMEM columns.
+// Every wait is bounded; a wait that gives up sets the status words, all roles drain, TMEM is freed.
+#include "afb_internal.h"
+#include "dequant.cuh"
+#include "ptx_sm100.cuh"
+
+namespace afb {
+
+namespace {
+
+constexpr int BNW = 128;      // output channels per tile = TMEM lanes
+constexpr int BK = 64;
+constexpr int kSlotsA = 6;    // TMEM slots of converted weights
+constexpr int kWorkerWarps = 8;   // measured: 8 beats 16 (1.10 vs 1.04 PFLOP/s on 2048 x 11008 x 4096)
+constexpr int kKParts = kWorkerWarps / 4;            // warps per TMEM lane quarter = parts the 64-wide K step is cut into
+constexpr int kKPer = BK / kKParts;                  // k per converter thread and stage (32 or 16)
+constexpr int kThreads = 32 * (2 + kWorkerWarps);   // 320
+
+struct TsParams {
+    uint16_t* c;
+    const void* scale;
+    uint32_t m, n, k, ldc;
+    uint32_t enc, scale_dtype, group;
+    uint32_t m_tiles, n_tiles;
+    uint32_t c_f32;
+    int32_t* status;
+};
+
+template <int BITS, int BMA>
+struct TsLayout {
+    static constexpr int kStages = BMA == 256 ? 5 : 8;
+    static constexpr int kRawRowBytes = BK * BITS / 8;
+    static constexpr int kActBytes = BMA * BK * 2;              // 32 KiB at BMA = 256
+    static constexpr int kRawBytes = BNW * kRawRowBytes;         // 8 KiB (int8) / 4 KiB (int4)
+    static constexpr int kOffAct = 0;
+    static constexpr int kOffRaw = kStages * kActBytes;
+    static constexpr int kOffBars = kOffRaw + kStages * kRawBytes;
+    static constexpr int kNumBars = 3 * kStages + 2 * kSlotsA + 2;
+    static constexpr int kOffMisc = kOffBars + kNumBars * 8;
+    static constexpr int kDynamic = kOffMisc + 16 + 1024;
+    static constexpr uint32_t kTmemCols = 512;                   // accumulator [0, BMA) + weight slots [256, 256 + kSlotsA * 32)
+    static constexpr uint32_t kColA = 256;
+};
+
+__device__ __forceinline__ void report_timeout(int32_t* status, int where, int a, int b) {
+    if (atomicCAS(status, 0, AFB_ERR_TIMEOUT) == 0) { status[1] = where; status[2] = a; status[3] = b; }
+}
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = ptx::globaltimer();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xffu) == 0) {
+            if (*abort_flag) return false;
+            if (ptx::globaltimer() - t0 > ptx::kWaitLimitNs) return false;
+        }
+    }
+    return true;
+}
+
+template <int BITS, bool GROUPED, int BMA>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w, const TsParams p) {
+    using L = TsLayout<BITS, BMA>;
+    constexpr int S = L::kStages;
+    extern __shared__ uint8_t smem_raw_base[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw_base) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw_base + (smem_base - ptx::smem_u32(smem_raw_base));
+
+    const uint32_t bar_base = smem_base + L::kOffBars;
+    auto bar_full      = [&](int s) { return bar_base + 8u * s; };                       // TMA landed (act + raw)
+    auto bar_empty_act = [&](int s) { return bar_base + 8u * (S + s); };                 // MMA done with the activation tile
+    auto bar_empty_raw = [&](int s) { return bar_base + 8u * (2 * S + s); };             // converters done with the raw tile
+    auto bar_full_a    = [&](int s) { return bar_base + 8u * (3 * S + s); };             // converted weights are in TMEM slot s
+    auto bar_empty_a   = [&](int s) { return bar_base + 8u * (3 * S + kSlotsA + s); };   // MMA done with TMEM slot s
+    const uint32_t bar_acc_full = bar_base + 8u * (3 * S + 2 * kSlotsA);
+    const uint32_t bar_acc_empty = bar_acc_full + 8u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kOffMisc);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t num_kb = p.k / BK;
+    const uint32_t num_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty_act(s), 1); ptx::mbar_init(bar_empty_raw(s), kWorkerWarps); }
+        for (int s = 0; s < kSlotsA; ++s) { ptx::mbar_init(bar_full_a(s), kWorkerWarps); ptx::mbar_init(bar_empty_a(s), 1); }
+        ptx::mbar_init(bar_acc_full, 1);
+        ptx::mbar_init(bar_acc_empty, kWorkerWarps);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tmap_act);
+        ptx::prefetch_tmap(&tmap_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), L::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ======================= TMA producer =======================
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (int)(t % p.m_tiles) * BMA;
+                const int n0 = (int)(t / p.m_tiles) * BNW;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!wait_or_abort(bar_empty_act(stage), phase ^ 1u, abort_flag) ||
+                        !wait_or_abort(bar_empty_raw(stage), phase ^ 1u, abort_flag)) {
+                        if (!*abort_flag) { report_timeout(p.status, 21, (int)t, (int)kb); *abort_flag = 1; }
+                        ok = false; break;
+                    }
+                    ptx::mbar_arrive_expect_tx(bar_full(stage), L::kActBytes + L::kRawBytes);
+                    ptx::tma_load_2d(smem_base + L::kOffAct + stage * L::kActBytes, &tmap_act, (int)(kb * BK), m0, bar_full(stage));
+                    ptx::tma_load_2d(smem_base + L::kOffRaw + stage * L::kRawBytes, &tmap_w, (int)(kb * L::kRawRowBytes), n0, bar_full(stage));
+                    issued |= 1u << stage;
+                    issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+            for (int s = 0; s < S; ++s)   // never leave with a bulk copy still writing this CTA's shared memory
+                if (issued & (1u << s)) ptx::mbar_wait(bar_full(s), (issued_parity >> s) & 1u);
+        }
+    } else if (warp == 1) {
+        // ======================= MMA issuer =======================
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16_f32(BNW, BMA);
+            uint32_t st = 0, ph = 0, sa = 0, pa = 0, it = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                if (!wait_or_abort(bar_acc_empty, (it & 1u) ^ 1u, abort_flag)) {   // the epilogue of the previous tile has drained the accumulator
+                    if (!*abort_flag) { report_timeout(p.status, 22, (int)t, -1); *abort_flag = 1; }
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_full_a(sa), pa, abort_flag)) {
+                        if (!*abort_flag) { report_timeout(p.status, 23, (int)t, (int)kb); *abort_flag = 1; }
+                        ok = false; break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint64_t db = ptx::umma_desc_kmajor_sw128(smem_base + L::kOffAct + st * L::kActBytes);
+                    const uint32_t ta = tmem_base + L::kColA + sa * 32;
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j)   // 16 k per instruction: 8 TMEM columns of weights, 32 bytes of each activation row
+                        ptx::umma_bf16_ts(tmem_base, ta + 8 * j, db + 2u * j, idesc, (kb | (uint32_t)j) ? 1u : 0u);
+                    ptx::umma_commit(bar_empty_act(st));
+                    ptx::umma_commit(bar_empty_a(sa));
+                    if (++st == S) { st = 0; ph ^= 1u; }
+                    if (++sa == kSlotsA) { sa = 0; pa ^= 1u; }
+                }
+                if (ok) ptx::umma_commit(bar_acc_full);
+            }
+        }
+    } else {
+        // ======================= converters + epilogue =======================
+        const uint32_t q = (uint32_t)(warp & 3);             // TMEM lane quarter this warp may touch
+        const uint32_t kq = (uint32_t)(warp - 2) >> 2;        // which part of the 64-wide K step / which part of the columns
+        const uint32_t ch = q * 32 + lane;                    // channel (TMEM lane) of this thread inside the tile
+        const uint32_t xormask = (BITS == 8 && p.enc == AFB_ENC_OFFSET_BINARY) ? 0x80808080u : 0u;
+        const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
+        const uint32_t groups_per_row = GROUPED ? p.k / p.group : 0;
+        const uint32_t kb_per_group = GROUPED ? p.group / BK : 1;
+        // raw tile in shared memory: rows of 64 (int8) / 32 (int4) bytes, stored by TMA with the 64- / 32-byte swizzle
+        // (16-byte piece index XOR row bits); this thread converts kKPer consecutive k of its row
+        constexpr int kRawPer = kKPer * BITS / 8;                 // bytes per thread and stage: 32/16 (int8), 16/8 (int4)
+        constexpr int kPieces = kRawPer >= 16 ? kRawPer / 16 : 1;  // 16-byte pieces (an 8-byte read stays inside one piece)
+        uint32_t raw_off[kPieces];
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const uint32_t byte = kq * kRawPer + i * 16;           // offset inside the row before the swizzle
+            const uint32_t piece = byte >> 4;
+            raw_off[i] = BITS == 8 ? ch * 64 + ((piece ^ ((ch >> 1) & 3)) << 4) + (byte & 15)
+                                   : ch * 32 + ((piece ^ ((ch >> 2) & 1)) << 4) + (byte & 15);
+        }
+        uint32_t st = 0, ph = 0, sa = 0, pa = 0, it = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const uint32_t m0 = (t % p.m_tiles) * BMA, n0 = (t / p.m_tiles) * BNW;
+            const uint32_t nn = n0 + ch;
+            uint32_t sc_cur = 0, sc_nxt = 0;
+            auto load_gscale = [&](uint32_t gidx) -> uint32_t {
+                if (nn >= p.n || gidx >= groups_per_row) return (uint32_t)0;
+                return bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
+            };
+            if (GROUPED) sc_nxt = load_gscale(0);
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                if (GROUPED && (kb % kb_per_group) == 0) { sc_cur = sc_nxt; sc_nxt = load_gscale(kb / kb_per_group + 1); }
+                if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_empty_a(sa), pa ^ 1u, abort_flag)) {
+                    if (!*abort_flag) { report_timeout(p.status, 24, (int)t, (int)kb); *abort_flag = 1; }
+                    ok = false; break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint8_t* raw = smem_gen + L::kOffRaw + st * L::kRawBytes;
+                constexpr int kWords = kRawPer / 4;     // 32-bit words of raw weights per thread
+                constexpr int kOut = kKPer / 2;         // packed bf16 pairs = TMEM columns per thread
+                uint32_t w[kWords], o[kOut];
+                if (kRawPer >= 16) {
+#pragma unroll
+                    for (int i = 0; i < kPieces; ++i) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(raw + raw_off[i]);
+                        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                    }
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2*>(raw + raw_off[0]);
+                    w[0] = v.x; w[1] = v.y;
+                }
+#pragma unroll
+                for (int j = 0; j < kWords; ++j) {
+                    if (BITS == 8) {
+                        s8x4_to_bf16_natural(w[j] ^ xormask, o[2 * j], o[2 * j + 1]);
+                    } else {
+                        uint32_t qv[4];
+                        s4x8_to_bf16_natural(w[j], magic4, qv);
+                        o[4 * j] = qv[0]; o[4 * j + 1] = qv[1]; o[4 * j + 2] = qv[2]; o[4 * j + 3] = qv[3];
+                    }
+                }
+                if (GROUPED) {
+#pragma unroll
+                    for (int j = 0; j < kOut; ++j) o[j] = bf16x2_mul(o[j], sc_cur);
+                }
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + L::kColA + sa * 32 + kq * kOut;
+                ptx::tmem_st_cols(taddr, o);
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) { ptx::mbar_arrive(bar_full_a(sa)); ptx::mbar_arrive(bar_empty_raw(st)); }
+                if (++st == S) { st = 0; ph ^= 1u; }
+                if (++sa == kSlotsA) { sa = 0; pa ^= 1u; }
+            }
+            if (!ok) break;
+            // ---- epilogue of this tile: the accumulator is complete once the last MMA has been committed ----
+            if (!wait_or_abort(bar_acc_full, it & 1u, abort_flag)) {
+                if (!*abort_flag) { report_timeout(p.status, 25, (int)t, -1); *abort_flag = 1; }
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            float scale = 1.f;
+            if (!GROUPED && nn < p.n)
+                scale = p.scale_dtype == AFB_SCALE_BF16 ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(p.scale)[nn] << 16)
+                                                       : reinterpret_cast<const float*>(p.scale)[nn];
+            constexpr int kColsPerWarp = BMA / kKParts;   // the warps of a lane quarter split the activation rows
+#pragma unroll 1
+            for (int c0 = 0; c0 < kColsPerWarp; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t col = kq * kColsPerWarp + c0;
+                ptx::tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + col, r);
+                ptx::tmem_ld_wait();
+                if (nn < p.n) {
+                    const uint32_t mrow = m0 + col;
+                    if (p.c_f32) {
+                        float* dst = reinterpret_cast<float*>(p.c) + (size_t)mrow * p.ldc + nn;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (mrow + j < p.m) dst[(size_t)j * p.ldc] = __uint_as_float(r[j]) * scale;
+                    } else {
+                        uint16_t* dst = p.c + (size_t)mrow * p.ldc + nn;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (mrow + j < p.m) dst[(size_t)j * p.ldc] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j]) * scale));
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
+        }
+    }
+
+    // ---- teardown: every thread gets here, also after an abort ----
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, L::kTmemCols);
+    }
+}
+
+int ts_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+               uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return AFB_ERR_CUDA;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? AFB_OK : AFB_ERR_CUDA;
+}
+
+template <int BITS, bool GROUPED, int BMA>
+int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
+    using L = TsLayout<BITS, BMA>;
+    static_assert(L::kDynamic <= 232448, "shared memory budget");
+    CUtensorMap ta, tw;
+    int rc = ts_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.ptr_a, a.k, a.m, (uint64_t)a.lda * 2, BK, BMA, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint64_t row_bytes = (uint64_t)a.k * BITS / 8, ld_bytes = (uint64_t)a.ldb * BITS / 8;
+    rc = ts_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.ptr_b, row_bytes, a.n, ld_bytes, L::kRawRowBytes, BNW,
+                    BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc) return rc;
+    TsParams p;
+    p.c = reinterpret_cast<uint16_t*>(a.ptr_c);
+    p.scale = a.ptr_scale;
+    p.m = a.m; p.n = a.n; p.k = a.k; p.ldc = a.ldc;
+    p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
+    p.m_tiles = (a.m + BMA - 1) / BMA;
+    p.n_tiles = (a.n + BNW - 1) / BNW;
+    p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
+    p.status = ctx->status;
+    auto kern = prefill_ts_kernel<BITS, GROUPED, BMA>;
+    static int attr_dev = -1;  // per template instance
+    if (attr_dev != ctx->device) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+        if (e != cudaSuccess) return cuda_fail(e);
+        attr_dev = ctx->device;
+    }
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    kern<<<grid, kThreads, L::kDynamic, s>>>(ta, tw, p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
+}  // namespace
+
+int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
+    if (!prefill_supports(a)) return AFB_ERR_UNSUPPORTED;
+    const bool grouped = a.group_size != 0;
+    const bool wide = a.m > 128;   // activation rows per tile: 256, or 128 when M is small
+    if (a.b_bits == 8) {
+        if (wide) return grouped ? launch_ts_cfg<8, true, 256>(a, ctx, s) : launch_ts_cfg<8, false, 256>(a, ctx, s);
+        return grouped ? launch_ts_cfg<8, true, 128>(a, ctx, s) : launch_ts_cfg<8, false, 128>(a, ctx, s);
+    }
+    if (wide) return grouped ? launch_ts_cfg<4, true, 256>(a, ctx, s) : launch_ts_cfg<4, false, 256>(a, ctx, s);
+    return grouped ? launch_ts_cfg<4, true, 128>(a, ctx, s) : launch_ts_cfg<4, false, 128>(a, ctx, s);
+}
+
+}  // namespace afb

@@ -173,8 +173,9 @@ int main(int argc, char** argv) {
     if (o.validation) {
         gemm_ref(static_cast<float*>(c_host_buf.GetBuffer()), a_f32, b_f32, s_f32, m, n, k, o.lda, o.ldb, o.ldc, o.b_col, o.group);
         GPU_CHECK_ERROR(afb_memcpy_d2h(c_host_buf_from_device.GetBuffer(), c_device_buf.GetBuffer(), sizeof(CDataType) * c_elems));
-        // integer data must match to the reference's own 1e-3; real data to the 1e-2 contract (bf16 rounding alone is up to 2^-8)
-        const float nrms = o.real_data ? 5e-3f : 1e-3f, rel = o.real_data ? (o.group && chosen == AFB_VARIANT_PREFILL ? 1.5e-2f : 1e-2f) : 1e-3f;
+        // Integer data: products and sums are exact, so the only error is the final rounding of C to bf16 (at most 2^-8
+        // relative; the reference's own 1e-3 bound only holds while every |C| < 256 is an exact bf16).  Real data: the 1e-2 contract.
+        const float nrms = o.real_data ? 5e-3f : 2e-3f, rel = o.real_data ? (o.group && chosen == AFB_VARIANT_PREFILL ? 1.5e-2f : 1e-2f) : 4e-3f;
         const float floor_frac = (o.group && chosen == AFB_VARIANT_PREFILL) ? 1.0f : 0.05f;
         bool res = true;
         const float* ref = static_cast<const float*>(c_host_buf.GetBuffer());

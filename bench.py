@@ -352,7 +352,7 @@ def run_ours(args):
     # roofline of the dominant kernel (the prefill kernel of the up-projection: no exchange inside its events)
     up_flops = gemm_flops(mlp.m, mlp.up_n_local, mlp.up_k)
     achieved = up_flops / up_ms / 1e9
-    roofline = {"kernel": "prefill_kernel<8,false,256> (up-projection shard)", "bound": "tensor", "achieved": achieved,
+    roofline = {"kernel": "prefill_ts_kernel<8,false,256> (up-projection shard)", "bound": "tensor", "achieved": achieved,
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                 "peak_source": f"{peaks['_source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
                 "frac_of_nominal": achieved / NOMINAL["bf16_tflops"], "avg_launch_ms": up_ms,

@@ -48,6 +48,8 @@ extern "C" {
 #define AFB_VARIANT_NAIVE   3u /* one thread per output element, fp32, order of host_ref.hpp:15-24 */
 
 #define AFB_FLAG_C_F32 1u /* C is fp32 [M,N] instead of bf16: prefill variant (partial sums of a K-split) and naive variant */
+#define AFB_FLAG_PREFILL_SMEM_B 2u /* prefill variant: force the form that stages the converted weights in shared memory */
+#define AFB_FLAG_PREFILL_TMEM_A 4u /* prefill variant: force the form that keeps the converted weights in tensor memory  */
 
 /*
  * Kernel argument block.  The first ten fields are the reference's packed kernarg

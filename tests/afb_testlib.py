@@ -251,10 +251,10 @@ class DeviceCase:
             self.lib.free(p)
 
 
-def run_case(lib, case, variant=0, c_f32=False, ldc=None, guard=0):
+def run_case(lib, case, variant=0, c_f32=False, ldc=None, guard=0, flags=0):
     dc = DeviceCase(lib, case, c_f32=c_f32, ldc=ldc, guard=guard)
     try:
-        lib.gemm_launch(dc.args(variant=variant, flags=1 if c_f32 else 0))
+        lib.gemm_launch(dc.args(variant=variant, flags=flags | (1 if c_f32 else 0)))
         lib.device_sync()
         out, raw = dc.result()
     finally:

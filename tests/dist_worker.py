@@ -99,8 +99,10 @@ def main():
         st = lib.read_status()
         assert st[0] == 0, f"device status {st}"
         assert all(np.array_equal(outs[0], o) for o in outs[1:]), "fused exchange is not repeatable"
-        mx, nrms, _ = oracle.compare(ref, outs[0], T.rms(ref) * 0.05)
-        assert mx <= 1e-2, f"fused {partial}: max rel err {mx}"
+        # fp32 partial sums: the usual bound.  bf16 partial sums are each rounded to 2^-9 of their OWN magnitude, which can
+        # exceed the magnitude of the total where the partial sums cancel: bounded against max(|ref|, RMS) instead.
+        mx, nrms, _ = oracle.compare(ref, outs[0], T.rms(ref) * (0.05 if partial == "f32" else 1.0))
+        assert mx <= 1e-2 and nrms < 3e-3, f"fused {partial}: max rel err {mx}, nrms {nrms}"
         # every rank holds the same bits
         t = torch.from_numpy(outs[0].astype(np.int32)).cuda()
         lo, hi = t.clone(), t.clone()

@@ -114,20 +114,26 @@ def test_decode_is_deterministic_and_leaves_workspace_clean(afb, oracle):
 PREFILL_SHAPES = [(128, 256, 64), (128, 256, 512), (17, 128, 256), (256, 512, 1024), (300, 264, 320), (128, 128, 4096), (640, 1280, 2048)]
 
 
+# the prefill variant has two forms; each is forced in turn so that both are covered whatever the default is
+IMPLS = [pytest.param(pkg.FLAG_PREFILL_SMEM_B, id="smem-b"), pytest.param(pkg.FLAG_PREFILL_TMEM_A, id="tmem-a")]
+
+
+@pytest.mark.parametrize("impl", IMPLS)
 @pytest.mark.parametrize("m,n,k", PREFILL_SHAPES)
 @pytest.mark.parametrize("enc", [0, 1])
-def test_prefill_int8_per_channel(afb, oracle, m, n, k, enc):
+def test_prefill_int8_per_channel(afb, oracle, m, n, k, enc, impl):
     case = T.make_case(m, n, k, bits=8, enc=enc, seed=n + k)
-    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL)
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=impl)
     check_close(oracle, oracle.gemm(case, threads=8), got, f"prefill int8 {m}x{n}x{k}")
     assert afb.read_status()[0] == 0
 
 
+@pytest.mark.parametrize("impl", IMPLS)
 @pytest.mark.parametrize("m,n,k", [(128, 256, 256), (200, 520, 1024), (384, 1024, 2048)])
 @pytest.mark.parametrize("bits,group,scale_dtype", [(4, 0, 0), (4, 128, 1), (8, 128, 1), (4, 64, 1), (8, 0, 1)])
-def test_prefill_int4_and_groups(afb, oracle, m, n, k, bits, group, scale_dtype):
+def test_prefill_int4_and_groups(afb, oracle, m, n, k, bits, group, scale_dtype, impl):
     case = T.make_case(m, n, k, bits=bits, group=group, scale_dtype=scale_dtype, seed=7 * m + k, scale_range=(0.005, 0.05))
-    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL)
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=impl)
     ref_exact = oracle.gemm(case, threads=8)
     if group:
         # tight check against the oracle fed with the SAME bf16-rounded weights the tensor cores see ...
@@ -143,20 +149,32 @@ def test_prefill_int4_and_groups(afb, oracle, m, n, k, bits, group, scale_dtype)
     assert afb.read_status()[0] == 0
 
 
+@pytest.mark.parametrize("impl", IMPLS)
+def test_prefill_fp32_output_for_k_split_partials(afb, oracle, impl):
+    """AFB_FLAG_C_F32: the fp32 accumulator times the scale, unrounded (what a K-split rank hands to the all-reduce)."""
+    case = T.make_case(300, 264, 512, seed=44)
+    got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, c_f32=True, flags=impl)
+    ref = oracle.gemm(case, threads=4)
+    assert np.abs(got - ref).max() <= 1e-4 * T.rms(ref)      # only the fp32 summation order differs
+
+
 # ---------------------------------------------------------------- known-answer cases (exact)
-@pytest.mark.parametrize("variant,m", [(pkg.VARIANT_DECODE, 16), (pkg.VARIANT_DECODE, 3), (pkg.VARIANT_PREFILL, 160), (pkg.VARIANT_NAIVE, 20)])
+@pytest.mark.parametrize("variant,m,flags", [(pkg.VARIANT_DECODE, 16, 0), (pkg.VARIANT_DECODE, 3, 0), (pkg.VARIANT_PREFILL, 160, pkg.FLAG_PREFILL_SMEM_B),
+                                             (pkg.VARIANT_PREFILL, 160, pkg.FLAG_PREFILL_TMEM_A), (pkg.VARIANT_PREFILL, 300, pkg.FLAG_PREFILL_TMEM_A),
+                                             (pkg.VARIANT_NAIVE, 20, 0)])
 @pytest.mark.parametrize("bits", [8, 4])
-def test_reference_style_integer_data_is_exact(afb, oracle, variant, m, bits):
+def test_reference_style_integer_data_is_exact(afb, oracle, variant, m, bits, flags):
     """The reference validates on integers in {-2,-1,0,1} (random_gen.hpp:24,37,50): every product and
     partial sum is exact, so any correct kernel must reproduce the oracle exactly after bf16 rounding."""
     case = T.make_case(m, 256, 512, bits=bits, seed=2, integer_data=True)
-    got, _ = T.run_case(afb, case, variant=variant)
-    assert np.array_equal(got, T.np_bf16_rne(oracle.gemm(case)))
+    got, _ = T.run_case(afb, case, variant=variant, flags=flags)
+    # compared as numbers: with a zero scale the kernels form (sum * 0), which may be -0 where the oracle's sum of (a * (b * 0)) is +0
+    assert np.array_equal(T.np_bf16_to_f32(got), T.np_bf16_to_f32(T.np_bf16_rne(oracle.gemm(case))))
 
 
-@pytest.mark.parametrize("variant,m", [(pkg.VARIANT_DECODE, 8), (pkg.VARIANT_PREFILL, 128)])
+@pytest.mark.parametrize("variant,m,flags", [(pkg.VARIANT_DECODE, 8, 0), (pkg.VARIANT_PREFILL, 128, pkg.FLAG_PREFILL_SMEM_B), (pkg.VARIANT_PREFILL, 256, pkg.FLAG_PREFILL_TMEM_A)])
 @pytest.mark.parametrize("bits", [8, 4])
-def test_one_hot_weights_select_activation_columns(afb, variant, m, bits):
+def test_one_hot_weights_select_activation_columns(afb, variant, m, bits, flags):
     n, k = 128, 256
     case = T.make_case(m, n, k, bits=bits, seed=9)
     q = np.zeros((n, k), np.int32)
@@ -165,27 +183,29 @@ def test_one_hot_weights_select_activation_columns(afb, variant, m, bits):
     u = q & (0xFF if bits == 8 else 0xF)
     case.b = np.ascontiguousarray(u.astype(np.uint8) if bits == 8 else (u[:, 0::2] | (u[:, 1::2] << 4)).astype(np.uint8))
     case.scale = np.ones(n, np.float32)
-    got, _ = T.run_case(afb, case, variant=variant)
+    got, _ = T.run_case(afb, case, variant=variant, flags=flags)
     assert np.array_equal(got, case.a[:, sel])      # scale 1, weight 1: C = selected columns of A, exactly
 
 
-@pytest.mark.parametrize("variant,m", [(pkg.VARIANT_DECODE, 4), (pkg.VARIANT_PREFILL, 128)])
+@pytest.mark.parametrize("variant,m,flags", [(pkg.VARIANT_DECODE, 4, 0), (pkg.VARIANT_PREFILL, 128, pkg.FLAG_PREFILL_SMEM_B), (pkg.VARIANT_PREFILL, 130, pkg.FLAG_PREFILL_TMEM_A)])
 @pytest.mark.parametrize("bits,val", [(8, -128), (8, 127), (4, -8), (4, 7)])
-def test_extreme_weights_sign_extension(afb, oracle, variant, m, bits, val):
+def test_extreme_weights_sign_extension(afb, oracle, variant, m, bits, val, flags):
     case = T.make_case(m, 128, 256, bits=bits, seed=4)
     u = val & (0xFF if bits == 8 else 0xF)
     case.b[:] = u if bits == 8 else (u | (u << 4))
     case.q[:] = val
-    got, _ = T.run_case(afb, case, variant=variant)
+    got, _ = T.run_case(afb, case, variant=variant, flags=flags)
     check_close(oracle, oracle.gemm(case), got, f"all weights {val}")
 
 
 # ---------------------------------------------------------------- memory safety (no compute-sanitizer on this pool)
-@pytest.mark.parametrize("variant,m,n,k", [(pkg.VARIANT_DECODE, 5, 264, 512), (pkg.VARIANT_PREFILL, 130, 264, 256), (pkg.VARIANT_NAIVE, 5, 70, 64)])
-def test_guard_bytes_and_padding_untouched(afb, oracle, variant, m, n, k):
+@pytest.mark.parametrize("variant,m,n,k,flags", [(pkg.VARIANT_DECODE, 5, 264, 512, 0), (pkg.VARIANT_PREFILL, 130, 264, 256, pkg.FLAG_PREFILL_SMEM_B),
+                                                 (pkg.VARIANT_PREFILL, 130, 264, 256, pkg.FLAG_PREFILL_TMEM_A), (pkg.VARIANT_PREFILL, 259, 136, 128, pkg.FLAG_PREFILL_TMEM_A),
+                                                 (pkg.VARIANT_NAIVE, 5, 70, 64, 0)])
+def test_guard_bytes_and_padding_untouched(afb, oracle, variant, m, n, k, flags):
     case = T.make_case(m, n, k, seed=6)
     ldc = n + 24
-    got, raw = T.run_case(afb, case, variant=variant, ldc=ldc, guard=4096)
+    got, raw = T.run_case(afb, case, variant=variant, ldc=ldc, guard=4096, flags=flags)
     check_close(oracle, oracle.gemm(case), got, "padded C")
     assert np.all(raw[:4096] == 0xCD) and np.all(raw[-4096:] == 0xCD)
     body = raw[4096:-4096].view(np.uint16)
