@@ -133,6 +133,98 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Tile-granular form: runs NEXT TO the K-split GEMM (launched after it, on another stream).  The GEMM counts every
+// finished tile of its partial sum in tile_done[t]; this kernel takes the tiles this rank owns (t % world == rank) in
+// the order the GEMM produces them, waits until all ranks have counted the tile, then pulls, adds, rounds and pushes it.
+// The exchange of a tile thus overlaps the GEMM main loop of the following tiles.  The GEMM never waits for this kernel.
+// ---------------------------------------------------------------------------------------------------------
+struct TileARParams {
+    ARParams ar;
+    const uint32_t* tile_done[AFB_MAX_RANKS];
+    uint32_t tile_m, tile_n, m_tiles, n_tiles, arrivals;
+};
+constexpr int kTileThreads = 256;
+constexpr int kSubRows = 64;   // rows of a tile handled as one unit of work
+
+__global__ void __launch_bounds__(kTileThreads, 2) ksplit_tile_allreduce_kernel(const TileARParams tp) {
+    const ARParams& p = tp.ar;
+    __shared__ uint32_t s_ok;
+    __shared__ uint32_t s_last;
+    const uint32_t tiles = tp.m_tiles * tp.n_tiles;
+    const uint32_t owned = tiles > p.rank ? (tiles - p.rank + p.world - 1) / p.world : 0;
+    const uint32_t subs = tp.tile_m / kSubRows;
+    const uint32_t units = owned * subs;
+    const uint32_t want = tp.arrivals * p.epoch;
+    const uint32_t vec_per_row = tp.tile_n / 8;                    // 8 channels (32 bytes of fp32) per thread
+    const uint32_t rows_per_pass = kTileThreads / vec_per_row;
+    bool failed = false;
+    for (uint32_t u = blockIdx.x; u < units && !failed; u += gridDim.x) {
+        const uint32_t t = p.rank + (u / subs) * p.world, sub = u % subs;
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = now_ns();
+            bool ok = true;
+            for (uint32_t q = 0; q < p.world && ok; ++q) {
+                uint32_t spins = 0;
+                while ((int32_t)(ld_acquire_sys(tp.tile_done[q] + t) - want) < 0) {
+                    if ((++spins & 0xfu) == 0) {
+                        if (now_ns() - t0 > p.wait_ns) { ok = false; break; }
+                        __nanosleep(200);
+                    }
+                }
+            }
+            if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 12; p.status[2] = (int)t; p.status[3] = (int)p.epoch; }
+            s_ok = ok ? 1u : 0u;
+        }
+        __syncthreads();
+        if (!s_ok) { failed = true; break; }
+        const uint32_t m0 = (t % tp.m_tiles) * tp.tile_m + sub * kSubRows, n0 = (t / tp.m_tiles) * tp.tile_n;
+        const uint32_t col = n0 + (threadIdx.x % vec_per_row) * 8;
+        for (uint32_t r = threadIdx.x / vec_per_row; r < (uint32_t)kSubRows; r += rows_per_pass) {
+            const uint32_t row = m0 + r;
+            if (row >= p.m || col >= p.n) continue;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            uint4 lo[AFB_MAX_RANKS], hi[AFB_MAX_RANKS];
+#pragma unroll
+            for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                if (q < (int)p.world) {
+                    const float* src = reinterpret_cast<const float*>(p.partial[q]) + (size_t)row * p.ld_partial + col;
+                    lo[q] = ld16(src); hi[q] = ld16(src + 4);
+                }
+#pragma unroll
+            for (int q = 0; q < AFB_MAX_RANKS; ++q)   // fixed rank order: identical bits wherever it is computed
+                if (q < (int)p.world) {
+                    acc[0] += __uint_as_float(lo[q].x); acc[1] += __uint_as_float(lo[q].y); acc[2] += __uint_as_float(lo[q].z); acc[3] += __uint_as_float(lo[q].w);
+                    acc[4] += __uint_as_float(hi[q].x); acc[5] += __uint_as_float(hi[q].y); acc[6] += __uint_as_float(hi[q].z); acc[7] += __uint_as_float(hi[q].w);
+                }
+            const uint4 out = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+#pragma unroll
+            for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                if (q < (int)p.world) *reinterpret_cast<uint4*>(p.c[q] + (size_t)row * p.ldc + col) = out;
+        }
+        __syncthreads();   // s_ok is rewritten by the next unit
+    }
+    // the last CTA to finish tells every rank that this rank's tiles are in place, then waits for theirs
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (failed) atomicExch(p.cta_done + 1, 1u);
+        const uint32_t old = atomicAdd(p.cta_done, 1u);
+        s_last = old == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        const bool any_failed = atomicExch(p.cta_done + 1, 0u) != 0;
+        *p.cta_done = 0u;
+        __threadfence_system();
+        if (!any_failed) {   // after a timeout some tiles were not stored: do not claim completion
+            for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 1 * AFB_MAX_RANKS + p.rank, p.epoch);
+            const bool ok = wait_all(p.signals[p.rank], 1, p.world, p.epoch, p.wait_ns);
+            if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 13; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(uint16_t* __restrict__ dst, const float* __restrict__ src, uint32_t rows,
                                                             uint32_t cols, uint32_t ld_dst, uint32_t ld_src) {
     const uint32_t vec_per_row = cols / 8;
@@ -146,7 +238,8 @@ __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(uint16_t* __restrict
     }
 }
 
-uint32_t* g_cta_done[32] = {nullptr};
+uint32_t* g_cta_done[32] = {nullptr};      // two words per device: CTAs finished, any-CTA-failed
+uint32_t* g_cta_done_tile[32] = {nullptr}; // the tile-granular kernel may overlap the plain one: its own pair
 
 }  // namespace
 }  // namespace afb
@@ -165,9 +258,9 @@ extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* st
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;
     if (!g_cta_done[ctx->device]) {
-        cudaError_t e = cudaMalloc(&g_cta_done[ctx->device], sizeof(uint32_t));
+        cudaError_t e = cudaMalloc(&g_cta_done[ctx->device], 2 * sizeof(uint32_t));
         if (e != cudaSuccess) return cuda_fail(e);
-        e = cudaMemset(g_cta_done[ctx->device], 0, sizeof(uint32_t));
+        e = cudaMemset(g_cta_done[ctx->device], 0, 2 * sizeof(uint32_t));
         if (e != cudaSuccess) return cuda_fail(e);
     }
     ARParams p;
@@ -194,6 +287,75 @@ extern "C" int afb_cast_f32_to_bf16(void* dst, const void* src, uint32_t rows, u
     if ((uintptr_t)dst % 16 || (uintptr_t)src % 16) return AFB_ERR_BAD_ARG;
     if (!current_ctx()) return AFB_ERR_NOT_INIT;
     cast_f32_bf16_kernel<<<592, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<uint16_t*>(dst), reinterpret_cast<const float*>(src), rows, cols, ld_dst, ld_src);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
+// ---- tile-granular exchange -----------------------------------------------------------------------------
+extern "C" int afb_ksplit_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* num_tiles, uint32_t* arrivals) {
+    if (!tile_m || !tile_n || !num_tiles || !arrivals || m == 0 || n == 0) return AFB_ERR_BAD_ARG;
+    uint32_t mt, nt;
+    prefill_ts_tile_info(m, n, tile_m, tile_n, &mt, &nt, arrivals);
+    *num_tiles = mt * nt;
+    return AFB_OK;
+}
+
+extern "C" int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_done, void* stream) {
+    if (!args || !tile_done || !args->ptr_a || !args->ptr_b || !args->ptr_c || !args->ptr_scale) return AFB_ERR_BAD_ARG;
+    if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;
+    if (args->lda < args->k || args->ldc < args->n || args->ldb < args->k || args->b_layout != AFB_LAYOUT_COL) return AFB_ERR_BAD_ARG;
+    if (!(args->flags & AFB_FLAG_C_F32)) return AFB_ERR_UNSUPPORTED;   // the partial sums travel as fp32
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    return launch_prefill_ts_tiles(*args, ctx, tile_done, (cudaStream_t)stream);
+}
+
+extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* ta, void* stream) {
+    if (!ta) return AFB_ERR_BAD_ARG;
+    const afb_allreduce_args* a = &ta->base;
+    if (a->world == 0 || a->world > AFB_MAX_RANKS || a->rank >= a->world) return AFB_ERR_BAD_ARG;
+    if (a->m == 0 || a->n == 0 || a->n % 8 || a->ldc % 8 || a->ld_partial % 8 || a->ld_partial < a->n || a->ldc < a->n) return AFB_ERR_BAD_ARG;
+    if (a->epoch == 0 || a->reserved != 0 || !a->partial_f32) return AFB_ERR_BAD_ARG;
+    uint32_t tm, tn, mt, nt, arr;
+    prefill_ts_tile_info(a->m, a->n, &tm, &tn, &mt, &nt, &arr);
+    for (uint32_t q = 0; q < a->world; ++q) {
+        if (!a->partial[q] || !a->c[q] || !a->signals[q] || !ta->tile_done[q]) return AFB_ERR_BAD_ARG;
+        if ((uintptr_t)a->partial[q] % 16 || (uintptr_t)a->c[q] % 16) return AFB_ERR_BAD_ARG;
+    }
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    if (!g_cta_done_tile[ctx->device]) {
+        cudaError_t e = cudaMalloc(&g_cta_done_tile[ctx->device], 2 * sizeof(uint32_t));
+        if (e != cudaSuccess) return cuda_fail(e);
+        e = cudaMemset(g_cta_done_tile[ctx->device], 0, 2 * sizeof(uint32_t));
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    TileARParams tp;
+    ARParams& p = tp.ar;
+    for (int q = 0; q < AFB_MAX_RANKS; ++q) {
+        const bool on = q < (int)a->world;
+        p.partial[q] = on ? a->partial[q] : nullptr;
+        p.c[q] = on ? reinterpret_cast<uint16_t*>(a->c[q]) : nullptr;
+        p.signals[q] = on ? a->signals[q] : nullptr;
+        tp.tile_done[q] = on ? ta->tile_done[q] : nullptr;
+    }
+    p.rank = a->rank; p.world = a->world; p.m = a->m; p.n = a->n; p.ld_partial = a->ld_partial; p.ldc = a->ldc;
+    p.partial_f32 = 1; p.epoch = a->epoch;
+    p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
+    p.cta_done = g_cta_done_tile[ctx->device];
+    p.status = ctx->status;
+    tp.tile_m = tm; tp.tile_n = tn; tp.m_tiles = mt; tp.n_tiles = nt; tp.arrivals = arr;
+    // One CTA per SM next to the GEMM's CTA (256 threads, no dynamic shared memory, <= 128 registers per thread).
+    // The GEMM needs the SM's largest shared-memory carve-out; an SM cannot change its carve-out while a CTA is resident,
+    // so this kernel asks for the same carve-out: whichever of the two reaches an SM first, the other can join it.
+    static int carveout_dev = -1;
+    if (carveout_dev != ctx->device) {
+        cudaError_t e = cudaFuncSetAttribute(ksplit_tile_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return cuda_fail(e);
+        carveout_dev = ctx->device;
+    }
+    ksplit_tile_allreduce_kernel<<<ctx->sm_count, kTileThreads, 0, (cudaStream_t)stream>>>(tp);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);

@@ -40,6 +40,7 @@ struct TsParams {
     uint32_t enc, scale_dtype, group;
     uint32_t m_tiles, n_tiles;
     uint32_t c_f32;
+    uint32_t* tile_done;   // optional: per-tile counters, +kWorkerWarps when a tile of C has been stored (system-scope release)
     int32_t* status;
 };
 
@@ -284,8 +285,12 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 }
             }
             ptx::tc_fence_before_sync();
+            if (p.tile_done) __threadfence_system();   // this lane's stores of the tile are visible to every GPU before the count below
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
+            if (lane == 0) {
+                ptx::mbar_arrive(bar_acc_empty);
+                if (p.tile_done) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.tile_done + t), "r"(1u) : "memory");
+            }
         }
     }
 
@@ -312,7 +317,7 @@ int ts_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint6
 }
 
 template <int BITS, bool GROUPED, int BMA>
-int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
+int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr) {
     using L = TsLayout<BITS, BMA>;
     static_assert(L::kDynamic <= 232448, "shared memory budget");
     CUtensorMap ta, tw;
@@ -330,6 +335,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
     p.m_tiles = (a.m + BMA - 1) / BMA;
     p.n_tiles = (a.n + BNW - 1) / BNW;
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
+    p.tile_done = tile_done;
     p.status = ctx->status;
     auto kern = prefill_ts_kernel<BITS, GROUPED, BMA>;
     static int attr_dev = -1;  // per template instance
@@ -347,6 +353,17 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
 }
 
 }  // namespace
+
+// Tiles of the 256-row form, as the tile-granular exchange sees them: tile t covers rows (t % m_tiles) * 256 .. and
+// channels (t / m_tiles) * 128 ..; every tile is counted kTileArrivals times in tile_done[t] per launch.
+void prefill_ts_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* m_tiles, uint32_t* n_tiles, uint32_t* arrivals) {
+    *tile_m = 256; *tile_n = BNW; *m_tiles = (m + 255) / 256; *n_tiles = (n + BNW - 1) / BNW; *arrivals = kWorkerWarps;
+}
+
+int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* tile_done, cudaStream_t s) {
+    if (!prefill_supports(a) || a.group_size != 0 || a.b_bits != 8 || a.m <= 128) return AFB_ERR_UNSUPPORTED;   // the row-parallel path: int8, per-channel
+    return launch_ts_cfg<8, false, 256>(a, ctx, s, tile_done);
+}
 
 int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
     if (!prefill_supports(a)) return AFB_ERR_UNSUPPORTED;

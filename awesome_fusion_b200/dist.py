@@ -49,6 +49,11 @@ class AllReduceArgs(ctypes.Structure):
                 ("wait_ms", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
+class TileAllReduceArgs(ctypes.Structure):
+    """``afb_tile_allreduce_args`` of include/afb_capi.h."""
+    _fields_ = [("base", AllReduceArgs), ("tile_done", ctypes.c_void_p * MAX_RANKS)]
+
+
 class PeerExchange:
     """Buffers of the fused K-split all-reduce, shared between the ranks of one box by CUDA IPC.
 
@@ -65,17 +70,23 @@ class PeerExchange:
         self.c = lib.malloc(m * n * 2)
         self.signals = lib.malloc(2 * MAX_RANKS * 4)
         lib.memset(self.signals, 0, 2 * MAX_RANKS * 4)
+        # per-tile completion counters of the tile-granular form (fp32 partial sums only)
+        tm, tn, nt, arr = (ctypes.c_uint32() for _ in range(4))
+        lib.check(lib.lib.afb_ksplit_tile_info(m, n, ctypes.byref(tm), ctypes.byref(tn), ctypes.byref(nt), ctypes.byref(arr)), "afb_ksplit_tile_info")
+        self.num_tiles = nt.value
+        self.tile_done = lib.malloc(self.num_tiles * 4)
+        lib.memset(self.tile_done, 0, self.num_tiles * 4)
         lib.device_sync()
         self._imported = []
-        self.partials, self.cs, self.sigs = [None] * world, [None] * world, [None] * world
+        self.partials, self.cs, self.sigs, self.tds = [None] * world, [None] * world, [None] * world, [None] * world
         self.ok = True
         if world == 1:
-            self.partials[0], self.cs[0], self.sigs[0] = self.partial, self.c, self.signals
+            self.partials[0], self.cs[0], self.sigs[0], self.tds[0] = self.partial, self.c, self.signals, self.tile_done
             return
         # No rank may raise between the collectives below (the others would wait for it for ever):
         # failures are recorded, exchanged, and every rank reaches the same verdict.
         try:
-            mine = (lib.ipc_export(self.partial), lib.ipc_export(self.c), lib.ipc_export(self.signals))
+            mine = (lib.ipc_export(self.partial), lib.ipc_export(self.c), lib.ipc_export(self.signals), lib.ipc_export(self.tile_done))
         except Exception as e:  # noqa: BLE001
             mine, self.error = None, str(e)
         everyone = [None] * world
@@ -84,15 +95,15 @@ class PeerExchange:
             self.ok = False
         else:
             try:
-                for q, (hp, hc, hs) in enumerate(everyone):
+                for q, handles in enumerate(everyone):
                     if q == rank:
-                        self.partials[q], self.cs[q], self.sigs[q] = self.partial, self.c, self.signals
+                        self.partials[q], self.cs[q], self.sigs[q], self.tds[q] = self.partial, self.c, self.signals, self.tile_done
                     else:
                         ptrs = []
-                        for h in (hp, hc, hs):
+                        for h in handles:
                             ptrs.append(lib.ipc_import(h))
                             self._imported.append(ptrs[-1])
-                        self.partials[q], self.cs[q], self.sigs[q] = ptrs
+                        self.partials[q], self.cs[q], self.sigs[q], self.tds[q] = ptrs
             except Exception as e:  # noqa: BLE001
                 self.ok, self.error = False, str(e)
         verdicts = [None] * world
@@ -115,11 +126,31 @@ class PeerExchange:
         self.lib.lib.afb_ksplit_allreduce_launch.argtypes = [ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
         self.lib.check(self.lib.lib.afb_ksplit_allreduce_launch(ctypes.byref(a), stream), "afb_ksplit_allreduce_launch")
 
+    def gemm_publishing_tiles(self, args, stream=None):
+        """The K-split GEMM into this rank's partial-sum buffer, counting finished tiles for allreduce_tiles()."""
+        f = self.lib.lib.afb_gemm_launch_tiles
+        from .capi import GemmArgs
+        f.argtypes = [ctypes.POINTER(GemmArgs), ctypes.c_void_p, ctypes.c_void_p]
+        self.lib.check(f(ctypes.byref(args), self.tile_done, stream), "afb_gemm_launch_tiles")
+
+    def allreduce_tiles(self, stream=None):
+        """Tile-granular exchange; launch it AFTER gemm_publishing_tiles() of the same step, on another stream."""
+        assert self.partial_f32
+        self.epoch += 1
+        ta = TileAllReduceArgs()
+        ta.base = self.args()
+        ta.base.epoch = self.epoch
+        for q in range(self.world):
+            ta.tile_done[q] = self.tds[q]
+        f = self.lib.lib.afb_ksplit_tile_allreduce_launch
+        f.argtypes = [ctypes.POINTER(TileAllReduceArgs), ctypes.c_void_p]
+        self.lib.check(f(ctypes.byref(ta), stream), "afb_ksplit_tile_allreduce_launch")
+
     def close(self):
         self.lib.device_sync()
         for p in self._imported:
             self.lib.ipc_release(p)
-        for p in (self.partial, self.c, self.signals):
+        for p in (self.partial, self.c, self.signals, self.tile_done):
             self.lib.free(p)
 
 
@@ -132,7 +163,8 @@ def cast_f32_to_bf16(lib, dst, src, rows, cols, stream=None):
 class ShardedMLP:
     """The sharded benchmark step: column-parallel up-projection + row-parallel down-projection (int8, per-channel).
 
-    exchange: "fused" | "nccl" | "auto" (fused when the box shares memory between the processes, else nccl).
+    exchange: "overlap" (tile-granular exchange next to the GEMM) | "fused" (one exchange kernel after the GEMM) | "nccl" |
+              "auto" (overlap when the box shares memory between the processes, else nccl).
     partial:  "f32" (exact, ordered sum) | "bf16" (half the NVLink bytes; each partial rounded once)."""
 
     def __init__(self, lib, torch, rank=0, world=1, exchange="auto", partial="f32", m=4096, up=(28672, 8192), down=(8192, 28672), seed=0):
@@ -167,19 +199,25 @@ class ShardedMLP:
         self.tdist = tdist
         mode = exchange
         if mode == "auto":
+            mode = "overlap" if partial == "f32" else "fused"
+        self.overlap = mode == "overlap"
+        if mode == "overlap":
             mode = "fused"
+            self.side = torch.cuda.Stream()
         if mode == "fused":
             self.px = PeerExchange(lib, tdist, rank, world, m, down_n, partial_f32=(partial == "f32"))
             if not self.px.ok:
                 why = getattr(self.px, "error", "a peer could not share its memory")
                 self.px.close(); self.px = None
-                if exchange == "fused":
+                self.overlap = False
+                if exchange in ("fused", "overlap"):
                     raise pkg.AfbError(-3, "peer-memory exchange unavailable", why)
                 if rank == 0:
                     print(f"peer memory unavailable ({why}); using the NCCL exchange", flush=True)
                 mode = "nccl"
         if mode == "fused":
-            self.exchange_name = f"fused peer-memory all-reduce ({partial} partial sums)"
+            self.exchange_name = (f"tile-granular peer-memory all-reduce overlapped with the GEMM ({partial} partial sums)" if self.overlap
+                                  else f"fused peer-memory all-reduce after the GEMM ({partial} partial sums)")
             flags = 0 if partial == "bf16" else pkg.FLAG_C_F32
             self.args_down = lib.make_args(self.px.partial, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local, flags=flags)
         else:
@@ -196,6 +234,18 @@ class ShardedMLP:
         lib.gemm_launch(self.args_up, stream)
         if events:
             events[1].record()
+        if self.world > 1 and self.px is not None and self.overlap:
+            torch = self.torch
+            before = torch.cuda.current_stream().record_event()
+            self.px.gemm_publishing_tiles(self.args_down, stream)
+            with torch.cuda.stream(self.side):      # launched after the GEMM, runs next to it
+                self.side.wait_event(before)        # no point in polling while the previous GEMM still runs
+                self.px.allreduce_tiles(self.side.cuda_stream)
+                done = self.side.record_event()
+            torch.cuda.current_stream().wait_event(done)   # the step ends when C is complete on this rank
+            if events:
+                events[2].record()
+            return
         lib.gemm_launch(self.args_down, stream)
         if self.world > 1:
             if self.px is not None:

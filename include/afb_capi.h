@@ -163,6 +163,20 @@ typedef struct afb_allreduce_args {
     uint32_t  reserved;
 } afb_allreduce_args;
 int afb_ksplit_allreduce_launch(const afb_allreduce_args* args, void* stream);
+/* Tile-granular form of the same exchange, fused with the K-split GEMM: afb_gemm_launch_tiles is the prefill GEMM
+ * (int8, per-channel scales, fp32 partial sums, M > 128) that also adds `arrivals` to tile_done[t] when tile t of its
+ * output is stored (release at system scope; counters only grow, start them at zero).  afb_ksplit_tile_allreduce_launch,
+ * launched AFTER it on another stream, handles the tiles this rank owns (t % world == rank) as soon as every rank has
+ * counted them (tile_done[r][t] >= arrivals * epoch), so the NVLink traffic overlaps the GEMM main loop.  The GEMM never
+ * waits for the exchange kernel; if the two are serialised, launch order makes the GEMM run first.  Tile geometry and the
+ * number of counters come from afb_ksplit_tile_info.  Same signals, epochs and bounded waits as above. */
+typedef struct afb_tile_allreduce_args {
+    afb_allreduce_args base;                 /* partial_f32 must be 1 */
+    uint32_t*          tile_done[AFB_MAX_RANKS];
+} afb_tile_allreduce_args;
+int afb_ksplit_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* num_tiles, uint32_t* arrivals);
+int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_done, void* stream);
+int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* args, void* stream);
 /* fp32 [rows, cols] (ld_src) -> bf16 (ld_dst), round to nearest even: finishes a K-split whose partial
  * sums were combined by a library collective instead of afb_ksplit_allreduce_launch. */
 int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uint32_t cols, uint32_t ld_dst, uint32_t ld_src, void* stream);
