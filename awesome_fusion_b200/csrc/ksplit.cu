@@ -7,6 +7,7 @@
 // signals[phase][q] of every rank.  Phase 0: "my partial of this epoch is complete" (the GEMM that
 // produced it precedes this kernel in stream order).  Phase 1: "I have stored my row block into your C".
 // Epochs only grow, so nothing is ever reset and a late reader cannot mistake an old signal.
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include "afb_internal.h"
 
@@ -142,9 +143,10 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
 struct TileARParams {
     ARParams ar;
     const uint32_t* tile_done[AFB_MAX_RANKS];
-    uint32_t tile_m, tile_n, m_tiles, n_tiles, arrivals;
+    uint32_t tile_m, tile_n, m_tiles, n_tiles, arrivals, tile_epoch;
 };
-constexpr int kTileThreads = 256;
+constexpr int kTileThreads = 256;         // upper bound (launch bounds)
+constexpr int kTileThreadsDefault = 128;
 constexpr int kSubRows = 64;   // rows of a tile handled as one unit of work
 
 __global__ void __launch_bounds__(kTileThreads, 2) ksplit_tile_allreduce_kernel(const TileARParams tp) {
@@ -155,26 +157,30 @@ __global__ void __launch_bounds__(kTileThreads, 2) ksplit_tile_allreduce_kernel(
     const uint32_t owned = tiles > p.rank ? (tiles - p.rank + p.world - 1) / p.world : 0;
     const uint32_t subs = tp.tile_m / kSubRows;
     const uint32_t units = owned * subs;
-    const uint32_t want = tp.arrivals * p.epoch;
+    const uint32_t want = tp.arrivals * tp.tile_epoch;
     const uint32_t vec_per_row = tp.tile_n / 8;                    // 8 channels (32 bytes of fp32) per thread
-    const uint32_t rows_per_pass = kTileThreads / vec_per_row;
+    const uint32_t rows_per_pass = blockDim.x / vec_per_row;
     bool failed = false;
     for (uint32_t u = blockIdx.x; u < units && !failed; u += gridDim.x) {
         const uint32_t t = p.rank + (u / subs) * p.world, sub = u % subs;
-        if (threadIdx.x == 0) {
+        if (threadIdx.x < 32) {   // lane q watches rank q's counter: one NVLink round trip per poll, not one per rank
             const unsigned long long t0 = now_ns();
+            const uint32_t* f = threadIdx.x < p.world ? tp.tile_done[threadIdx.x] + t : nullptr;
             bool ok = true;
-            for (uint32_t q = 0; q < p.world && ok; ++q) {
-                uint32_t spins = 0;
-                while ((int32_t)(ld_acquire_sys(tp.tile_done[q] + t) - want) < 0) {
-                    if ((++spins & 0xfu) == 0) {
-                        if (now_ns() - t0 > p.wait_ns) { ok = false; break; }
-                        __nanosleep(200);
-                    }
+            uint32_t spins = 0;
+            while (true) {
+                const bool ready = f == nullptr || (int32_t)(ld_acquire_sys(f) - want) >= 0;
+                if (__all_sync(0xffffffffu, ready)) break;
+                if ((++spins & 0x7u) == 0) {
+                    const bool late = now_ns() - t0 > p.wait_ns;
+                    if (__any_sync(0xffffffffu, late)) { ok = false; break; }
+                    __nanosleep(100);
                 }
             }
-            if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 12; p.status[2] = (int)t; p.status[3] = (int)p.epoch; }
-            s_ok = ok ? 1u : 0u;
+            if (threadIdx.x == 0) {
+                if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 12; p.status[2] = (int)t; p.status[3] = (int)p.epoch; }
+                s_ok = ok ? 1u : 0u;
+            }
         }
         __syncthreads();
         if (!s_ok) { failed = true; break; }
@@ -316,7 +322,7 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
     const afb_allreduce_args* a = &ta->base;
     if (a->world == 0 || a->world > AFB_MAX_RANKS || a->rank >= a->world) return AFB_ERR_BAD_ARG;
     if (a->m == 0 || a->n == 0 || a->n % 8 || a->ldc % 8 || a->ld_partial % 8 || a->ld_partial < a->n || a->ldc < a->n) return AFB_ERR_BAD_ARG;
-    if (a->epoch == 0 || a->reserved != 0 || !a->partial_f32) return AFB_ERR_BAD_ARG;
+    if (a->epoch == 0 || a->reserved != 0 || !a->partial_f32 || ta->tile_epoch == 0 || ta->reserved != 0) return AFB_ERR_BAD_ARG;
     uint32_t tm, tn, mt, nt, arr;
     prefill_ts_tile_info(a->m, a->n, &tm, &tn, &mt, &nt, &arr);
     for (uint32_t q = 0; q < a->world; ++q) {
@@ -345,7 +351,7 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
     p.cta_done = g_cta_done_tile[ctx->device];
     p.status = ctx->status;
-    tp.tile_m = tm; tp.tile_n = tn; tp.m_tiles = mt; tp.n_tiles = nt; tp.arrivals = arr;
+    tp.tile_m = tm; tp.tile_n = tn; tp.m_tiles = mt; tp.n_tiles = nt; tp.arrivals = arr; tp.tile_epoch = ta->tile_epoch;
     // One CTA per SM next to the GEMM's CTA (256 threads, no dynamic shared memory, <= 128 registers per thread).
     // The GEMM needs the SM's largest shared-memory carve-out; an SM cannot change its carve-out while a CTA is resident,
     // so this kernel asks for the same carve-out: whichever of the two reaches an SM first, the other can join it.
@@ -355,7 +361,10 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
         if (e != cudaSuccess) return cuda_fail(e);
         carveout_dev = ctx->device;
     }
-    ksplit_tile_allreduce_kernel<<<ctx->sm_count, kTileThreads, 0, (cudaStream_t)stream>>>(tp);
+    // Few threads on purpose: the pulls are long-latency NVLink loads; a full-size CTA keeps so many of them in flight that the
+    // SM's load/store path backs up and the GEMM's own shared-memory reads queue behind them (measured: the GEMM ran 2.3x slower).
+    static const int threads = [] { const char* e = getenv("AFB_TILE_AR_THREADS"); const int v = e ? atoi(e) : 0; return (v == 32 || v == 64 || v == 128 || v == 256) ? v : kTileThreadsDefault; }();
+    ksplit_tile_allreduce_kernel<<<ctx->sm_count, threads, 0, (cudaStream_t)stream>>>(tp);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);

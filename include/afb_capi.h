@@ -167,12 +167,14 @@ int afb_ksplit_allreduce_launch(const afb_allreduce_args* args, void* stream);
  * (int8, per-channel scales, fp32 partial sums, M > 128) that also adds `arrivals` to tile_done[t] when tile t of its
  * output is stored (release at system scope; counters only grow, start them at zero).  afb_ksplit_tile_allreduce_launch,
  * launched AFTER it on another stream, handles the tiles this rank owns (t % world == rank) as soon as every rank has
- * counted them (tile_done[r][t] >= arrivals * epoch), so the NVLink traffic overlaps the GEMM main loop.  The GEMM never
+ * counted them (tile_done[r][t] >= arrivals * tile_epoch), so the NVLink traffic overlaps the GEMM main loop.  The GEMM never
  * waits for the exchange kernel; if the two are serialised, launch order makes the GEMM run first.  Tile geometry and the
  * number of counters come from afb_ksplit_tile_info.  Same signals, epochs and bounded waits as above. */
 typedef struct afb_tile_allreduce_args {
-    afb_allreduce_args base;                 /* partial_f32 must be 1 */
+    afb_allreduce_args base;                 /* partial_f32 must be 1; base.epoch orders the "block in place" signals */
     uint32_t*          tile_done[AFB_MAX_RANKS];
+    uint32_t           tile_epoch;           /* how many afb_gemm_launch_tiles have been issued on these counters (same on all ranks) */
+    uint32_t           reserved;
 } afb_tile_allreduce_args;
 int afb_ksplit_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* num_tiles, uint32_t* arrivals);
 int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_done, void* stream);
