@@ -33,11 +33,14 @@ constexpr int kWarps = 8;
 constexpr int kRing = 4;                       // cp.async stages per warp (power of two)
 constexpr int kStageBytes = 1024;              // 2 channels x 32 lanes x 16 bytes
 constexpr int kRingBytes = kWarps * kRing * kStageBytes;   // 32 KiB
-constexpr int kRedFloats = kWarps * 16 * 17;   // cross-warp reduction buffer, [warp][16 channels][<=16 rows + pad]
-constexpr int kActBytes = 32 * 1024;           // staged activations of one pass: m rows x (pass_k * 2 + 16) bytes
-constexpr int kOffRed = kRingBytes;
-constexpr int kOffAct = kOffRed + kRedFloats * 4 + 16;
-constexpr int kSmemBytes = kOffAct + kActBytes;   // 73.5 KiB: three CTAs per SM
+constexpr int kRedFloats = kWarps * 16 * 17;   // cross-warp reduction buffer, [warp][16 channels][<=16 rows + pad]; reuses the ring once the stream has ended
+// staged activations of one pass, m rows x (pass_k * 2 + 16) bytes: 20 KiB for m <= 8 (52 KiB per CTA: four CTAs per SM, 64 registers),
+// 40 KiB for m <= 16 (72 KiB per CTA: three CTAs per SM, 80 registers)
+__host__ __device__ constexpr int act_bytes(int mt) { return mt == 1 ? 20 * 1024 : 40 * 1024; }
+constexpr int kOffRed = 0;
+constexpr int kOffAct = kRingBytes;
+__host__ __device__ constexpr int smem_bytes(int mt) { return kOffAct + act_bytes(mt) + 16; }
+static_assert(kRedFloats * 4 <= kRingBytes, "the reduction buffer must fit the ring it reuses");
 
 struct DecodeParams {
     const uint16_t* a;
@@ -48,7 +51,7 @@ struct DecodeParams {
     uint32_t enc, scale_dtype, group;
     uint32_t wr;      // warps along the channel dimension (1, 2, 4 or 8); WK = 8 / wr
     uint32_t kc;      // k elements per slice (multiple of the chunk)
-    uint32_t pass_k;  // k elements staged per pass (multiple of chunk * WK; m * (pass_k * 2 + 16) <= kActBytes)
+    uint32_t pass_k;  // k elements staged per pass (multiple of chunk * WK; m * (pass_k * 2 + 16) <= act_bytes)
     uint32_t group_shift;  // log2(group) (groups are powers of two)
     uint32_t slices;  // gridDim.y
     float* ws;        // [slices][m][n] fp32 partial sums (slices > 1)
@@ -85,14 +88,14 @@ __device__ __forceinline__ float load_scale(const void* s, size_t idx, uint32_t 
 __device__ __forceinline__ uint32_t swz_piece(uint32_t pc) { return pc ^ (((pc >> 3) & 1u) << 1); }
 
 template <int BITS, int MT, bool GROUPED>
-__global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(const DecodeParams p) {
     constexpr int CH = BITS == 8 ? 64 : 128;    // k per chunk (a quad covers 64 bytes of one channel)
     constexpr int LK = CH / 4;                  // k per lane per chunk
     constexpr int AV = LK / 8;                  // 16-byte activation vectors per lane, row and chunk
 
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_red = reinterpret_cast<float*>(smem + kOffRed);
-    uint32_t* s_last = reinterpret_cast<uint32_t*>(smem + kOffRed + kRedFloats * 4);
+    uint32_t* s_last = reinterpret_cast<uint32_t*>(smem + kOffAct + act_bytes(MT));
     const uint32_t s_act = (uint32_t)__cvta_generic_to_shared(smem + kOffAct);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
@@ -244,6 +247,8 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams 
 
     // ---- reduce the WK warps that share 16 channels.  acc[mt][e]: channel = e < 2 ? g : g + 8, activation row = mt*8 + 2*tig + (e & 1)
     constexpr int MCOLS = 8 * MT;
+    cp_async_wait<0>();
+    __syncthreads();   // every warp is done with its ring slots: the reduction buffer takes their place
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -306,11 +311,11 @@ cudaError_t launch_one(const DecodeParams& p, dim3 grid, cudaStream_t s) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT));
         if (e != cudaSuccess) return e;
         attr_dev = dev;
     }
-    kern<<<grid, kThreads, kSmemBytes, s>>>(p);
+    kern<<<grid, kThreads, smem_bytes(MT), s>>>(p);
     return cudaGetLastError();
 }
 
@@ -342,7 +347,8 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, si
     const double weight_mb = (double)a.n * a.k * a.b_bits / 8 / 1e6;
     auto ctas = [&](uint32_t w) { return (a.n + 16 * w - 1) / (16 * w); };
     while (wr < 8 && ctas(wr * 2) >= 6 * sms) wr *= 2;              // plenty of channels: larger CTAs, fewer activation re-reads
-    while (wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > (size_t)kActBytes) wr *= 2;   // one round of the WK warps must fit the staging area
+    const size_t act_cap = (size_t)act_bytes(a.m <= 8 ? 1 : 2);
+    while (wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > act_cap) wr *= 2;   // one round of the WK warps must fit the staging area
     const uint32_t want = weight_mb < 48.0 ? sms * 3 / 2 : sms * 5;   // many small CTAs even out the load of the SMs (measured)
     uint32_t s = 1;
     const uint32_t unit = a.group_size > ch ? a.group_size : ch;
@@ -351,7 +357,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, si
     if (ctas(wr) > counter_count) s = 1;
     if (const char* e = getenv("AFB_DECODE_WR")) {       // tuning aid: force the CTA shape when it is legal
         const uint32_t v = (uint32_t)atoi(e);
-        if ((v == 1 || v == 2 || v == 4 || v == 8) && (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= (size_t)kActBytes) wr = v;
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= act_cap) wr = v;
     }
     if (const char* e = getenv("AFB_DECODE_SLICES")) {   // tuning aid: force the number of K-slices when it is legal
         const uint32_t v = (uint32_t)atoi(e);
@@ -360,7 +366,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, si
     p.wr = wr; p.slices = s; p.kc = a.k / s;
     // activations staged per pass: as many k as fit the staging area, in whole rounds of the WK warps
     const uint32_t round = ch * (kWarps / wr);
-    uint32_t pass_max = ((uint32_t)kActBytes / a.m - 16) / 2 / round * round;   // >= 512 k for m <= 16, round <= 512
+    uint32_t pass_max = ((uint32_t)act_cap / a.m - 16) / 2 / round * round;   // >= 512 k for m <= 16, round <= 512
     if (pass_max == 0) pass_max = round;
     const uint32_t npass = (p.kc + pass_max - 1) / pass_max;
     p.pass_k = ((p.kc + npass - 1) / npass + round - 1) / round * round;        // equal passes, whole rounds
