@@ -21,6 +21,9 @@ struct DeviceCtx {
     // staging for afb_gemm_host (grow-only)
     void*  stage[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t stage_bytes[4] = {0, 0, 0, 0};
+    // copy-in / copy-out streams and per-chunk events of the pipelined afb_gemm_host
+    cudaStream_t host_in = nullptr, host_out = nullptr;
+    cudaEvent_t host_ev[2 * 16 + 2] = {};
 };
 
 DeviceCtx* current_ctx();           // nullptr when afb_init was not called on the current device

@@ -124,6 +124,10 @@ int afb_finalize(void) {
     cudaDeviceSynchronize();
     cudaFree(c.status); cudaFree(c.splitk_ws); cudaFree(c.splitk_counters);
     for (int i = 0; i < 4; ++i) if (c.stage[i]) cudaFree(c.stage[i]);
+    if (c.host_in) {
+        cudaStreamDestroy(c.host_in); cudaStreamDestroy(c.host_out);
+        for (auto& e : c.host_ev) if (e) cudaEventDestroy(e);
+    }
     c = DeviceCtx();
     return AFB_OK;
 }
@@ -240,14 +244,59 @@ int afb_gemm_host(const afb_gemm_args* h, void* stream) {
         }
     }
     cudaStream_t s = (cudaStream_t)stream;
-    AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, s));
-    AFB_CUDA(cudaMemcpyAsync(ctx->stage[2], h->ptr_b, need[2], cudaMemcpyHostToDevice, s));
-    AFB_CUDA(cudaMemcpyAsync(ctx->stage[3], h->ptr_scale, need[3], cudaMemcpyHostToDevice, s));
     afb_gemm_args d = *h;
     d.ptr_c = ctx->stage[0]; d.ptr_a = ctx->stage[1]; d.ptr_b = ctx->stage[2]; d.ptr_scale = ctx->stage[3];
-    rc = afb_gemm_launch(&d, stream);
-    if (rc) return rc;
-    AFB_CUDA(cudaMemcpyAsync(h->ptr_c, ctx->stage[0], need[0], cudaMemcpyDeviceToHost, s));
+
+    // Pipelined form for B in [N,K] layout with per-channel scales: the channels are cut into chunks; while chunk i is
+    // multiplied, chunk i+1 of the weights travels host -> device and chunk i-1 of C travels device -> host (PCIe is full duplex).
+    constexpr uint32_t kChunks = 8;
+    const bool pipelined = h->b_layout == AFB_LAYOUT_COL && h->group_size == 0 && h->m > 16 && h->n >= kChunks * 512 && h->n % (kChunks * 128) == 0;
+    if (!pipelined) {
+        AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, s));
+        AFB_CUDA(cudaMemcpyAsync(ctx->stage[2], h->ptr_b, need[2], cudaMemcpyHostToDevice, s));
+        AFB_CUDA(cudaMemcpyAsync(ctx->stage[3], h->ptr_scale, need[3], cudaMemcpyHostToDevice, s));
+        rc = afb_gemm_launch(&d, stream);
+        if (rc) return rc;
+        AFB_CUDA(cudaMemcpyAsync(h->ptr_c, ctx->stage[0], need[0], cudaMemcpyDeviceToHost, s));
+        AFB_CUDA(cudaStreamSynchronize(s));
+        return AFB_OK;
+    }
+    if (!ctx->host_in) {
+        AFB_CUDA(cudaStreamCreateWithFlags(&ctx->host_in, cudaStreamNonBlocking));
+        AFB_CUDA(cudaStreamCreateWithFlags(&ctx->host_out, cudaStreamNonBlocking));
+        for (auto& e : ctx->host_ev) AFB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    cudaEvent_t* ev_in = ctx->host_ev;                 // [kChunks]: chunk i of B and scale is on the device
+    cudaEvent_t* ev_mm = ctx->host_ev + 16;            // [kChunks]: chunk i of C is computed
+    cudaEvent_t ev_start = ctx->host_ev[32], ev_end = ctx->host_ev[33];
+    AFB_CUDA(cudaEventRecord(ev_start, s));            // everything below happens after what the caller queued on `stream`
+    AFB_CUDA(cudaStreamWaitEvent(ctx->host_in, ev_start, 0));
+    AFB_CUDA(cudaStreamWaitEvent(ctx->host_out, ev_start, 0));
+    AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, ctx->host_in));
+    const uint32_t nc = h->n / kChunks;
+    const size_t ldb_bytes = (size_t)h->ldb * h->b_bits / 8, b_chunk = (size_t)nc * ldb_bytes;
+    for (uint32_t i = 0; i < kChunks; ++i) {
+        const size_t b_off = (size_t)i * b_chunk;
+        const size_t b_len = i + 1 < kChunks ? b_chunk : need[2] - b_off;
+        AFB_CUDA(cudaMemcpyAsync((char*)ctx->stage[2] + b_off, (const char*)h->ptr_b + b_off, b_len, cudaMemcpyHostToDevice, ctx->host_in));
+        AFB_CUDA(cudaMemcpyAsync((char*)ctx->stage[3] + (size_t)i * nc * scale_elt, (const char*)h->ptr_scale + (size_t)i * nc * scale_elt,
+                                 (size_t)nc * scale_elt, cudaMemcpyHostToDevice, ctx->host_in));
+        AFB_CUDA(cudaEventRecord(ev_in[i], ctx->host_in));
+        AFB_CUDA(cudaStreamWaitEvent(s, ev_in[i], 0));
+        afb_gemm_args c = d;
+        c.n = nc;
+        c.ptr_b = (char*)ctx->stage[2] + b_off;
+        c.ptr_scale = (char*)ctx->stage[3] + (size_t)i * nc * scale_elt;
+        c.ptr_c = (char*)ctx->stage[0] + (size_t)i * nc * c_elt;
+        rc = afb_gemm_launch(&c, stream);
+        if (rc) return rc;
+        AFB_CUDA(cudaEventRecord(ev_mm[i], s));
+        AFB_CUDA(cudaStreamWaitEvent(ctx->host_out, ev_mm[i], 0));
+        AFB_CUDA(cudaMemcpy2DAsync((char*)h->ptr_c + (size_t)i * nc * c_elt, (size_t)h->ldc * c_elt, (char*)ctx->stage[0] + (size_t)i * nc * c_elt,
+                                   (size_t)h->ldc * c_elt, (size_t)nc * c_elt, h->m, cudaMemcpyDeviceToHost, ctx->host_out));
+    }
+    AFB_CUDA(cudaEventRecord(ev_end, ctx->host_out));
+    AFB_CUDA(cudaStreamWaitEvent(s, ev_end, 0));
     AFB_CUDA(cudaStreamSynchronize(s));
     return AFB_OK;
 }

@@ -29,6 +29,11 @@ sys.path.insert(0, ROOT)
 
 METRIC = "bf16 x int GEMM throughput (2*M*N*K / time)"
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the up-projection on one GPU (ncu capture summarised in
+# profiles/launch_list_bench_n1.md): 634.0 MB + 223.4 MB
+UP_PROJ_DRAM_BYTES = 633972736 + 223373568
+# same for the decode kernel, int8 M=16 at 4096 x 4096 (profiles/decode_kernel_int8_m16_4096x4096.md)
+DECODE_M16_DRAM_BYTES = 16940800
 FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -356,7 +361,8 @@ def run_ours(args):
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                 "peak_source": f"{peaks['_source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
                 "frac_of_nominal": achieved / NOMINAL["bf16_tflops"], "avg_launch_ms": up_ms,
-                "traffic": None, "algorithmic_bytes": gemm_bytes(mlp.m, mlp.up_n_local, mlp.up_k, 8, 0)}
+                "traffic": UP_PROJ_DRAM_BYTES if world == 1 else None, "traffic_source": "profiles/launch_list_bench_n1.md" if world == 1 else None,
+                "algorithmic_bytes": gemm_bytes(mlp.m, mlp.up_n_local, mlp.up_k, 8, 0)}
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint8->fp32", "data": "synthetic",
             "config": {**headline_config(world), "exchange": mlp.exchange_name}, "clocks": clocks, "e2e": e2e_obj, "gpu_launches": launches,
@@ -371,7 +377,7 @@ def run_ours(args):
             d16 = next(c for c in cases if c["name"] == "decode-m16")
             line["roofline_decode"] = {"kernel": "decode_kernel<8,2,false>", "bound": "hbm", "achieved": d16["gbs"], "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": d16["gbs"] / peaks["hbm_gbs"], "peak_source": f"{peaks['_source']} copy bandwidth",
-                                       "traffic": None}
+                                       "traffic": DECODE_M16_DRAM_BYTES, "traffic_source": "profiles/decode_kernel_int8_m16_4096x4096.md"}
         if not args.no_cpu:
             v, info, _ = cpu_arm()
             line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}

@@ -216,14 +216,22 @@ def make_case(m, n, k, *, bits=8, group=0, layout=1, enc=0, scale_dtype=None, se
 class DeviceCase:
     """Device copies of a Case; frees them on close()."""
 
-    def __init__(self, lib, case, c_f32=False, ldc=None, guard=0):
+    def __init__(self, lib, case, c_f32=False, ldc=None, guard=0, lda=None, ldb=None):
         self.lib, self.case = lib, case
         self.ldc = ldc or case.n
+        self.lda = lda or case.k
+        self.ldb = ldb or case.ldb
         self.c_elt = 4 if c_f32 else 2
         self.guard = guard
         self.c_bytes = ((case.m - 1) * self.ldc + case.n) * self.c_elt
-        self.d_a = lib.to_device(case.a)
-        self.d_b = lib.to_device(case.b)
+        a_host, b_host = case.a, case.b
+        if self.lda != case.k:                       # rows of A padded to lda elements (padding filled with a recognisable pattern)
+            a_host = np.full((case.m, self.lda), 0x7FC0, np.uint16); a_host[:, :case.k] = case.a
+        if self.ldb != case.ldb:                     # rows of B padded to ldb elements (bytes for int8, nibbles for int4)
+            row_bytes = self.ldb * case.bits // 8
+            b_host = np.full((case.b.shape[0], row_bytes), 0x55, np.uint8); b_host[:, :case.b.shape[1]] = case.b
+        self.d_a = lib.to_device(a_host)
+        self.d_b = lib.to_device(b_host)
         self.d_s = lib.to_device(case.scale)
         self.d_c_base = lib.malloc(self.c_bytes + 2 * guard)
         lib.memset(self.d_c_base, 0xCD, self.c_bytes + 2 * guard)
@@ -231,7 +239,7 @@ class DeviceCase:
 
     def args(self, variant=0, flags=0):
         c = self.case
-        return self.lib.make_args(self.d_c, self.d_a, self.d_b, self.d_s, c.m, c.n, c.k, ldb=c.ldb, ldc=self.ldc, bits=c.bits,
+        return self.lib.make_args(self.d_c, self.d_a, self.d_b, self.d_s, c.m, c.n, c.k, lda=self.lda, ldb=self.ldb, ldc=self.ldc, bits=c.bits,
                                   encoding=c.enc, layout=c.layout, scale_dtype=c.scale_dtype, group=c.group, variant=variant,
                                   flags=flags)
 
@@ -251,8 +259,8 @@ class DeviceCase:
             self.lib.free(p)
 
 
-def run_case(lib, case, variant=0, c_f32=False, ldc=None, guard=0, flags=0):
-    dc = DeviceCase(lib, case, c_f32=c_f32, ldc=ldc, guard=guard)
+def run_case(lib, case, variant=0, c_f32=False, ldc=None, guard=0, flags=0, lda=None, ldb=None):
+    dc = DeviceCase(lib, case, c_f32=c_f32, ldc=ldc, guard=guard, lda=lda, ldb=ldb)
     try:
         lib.gemm_launch(dc.args(variant=variant, flags=flags | (1 if c_f32 else 0)))
         lib.device_sync()

@@ -213,6 +213,43 @@ def test_guard_bytes_and_padding_untouched(afb, oracle, variant, m, n, k, flags)
     assert np.all(full.reshape(m, ldc)[:, n:].reshape(-1)[:(m - 1) * 24] == 0xCDCD)   # the ldc padding columns
 
 
+@pytest.mark.parametrize("variant,m,flags", [(pkg.VARIANT_DECODE, 7, 0), (pkg.VARIANT_DECODE, 16, 0), (pkg.VARIANT_PREFILL, 96, pkg.FLAG_PREFILL_SMEM_B),
+                                             (pkg.VARIANT_PREFILL, 300, pkg.FLAG_PREFILL_TMEM_A), (pkg.VARIANT_NAIVE, 9, 0)])
+@pytest.mark.parametrize("bits", [8, 4])
+def test_leading_dimensions_larger_than_the_matrix(afb, oracle, variant, m, flags, bits):
+    """lda / ldb / ldc as the reference driver takes them on its command line (bfAintBGemm.cc:49-58): rows padded in memory."""
+    case = T.make_case(m, 264, 640, bits=bits, seed=31)
+    got, _ = T.run_case(afb, case, variant=variant, flags=flags, lda=640 + 64, ldb=640 + 128, ldc=264 + 8)
+    check_close(oracle, oracle.gemm(case, threads=4), got, f"padded leading dimensions, int{bits}")
+
+
+def test_gemm_publishing_tiles_and_tile_exchange_on_one_rank(afb, oracle):
+    """The tile-granular K-split exchange with a single rank: the GEMM counts its tiles, the exchange kernel waits for the
+    counts, rounds the fp32 partial sums to bf16 and stores C.  (Several ranks: tests/test_dist.py on a multi-GPU box.)"""
+    from awesome_fusion_b200 import dist as D
+    case = T.make_case(300, 264, 512, seed=51)
+    px = D.PeerExchange(afb, None, 0, 1, case.m, case.n, partial_f32=True)
+    d_a, d_b, d_s = afb.to_device(case.a), afb.to_device(case.b), afb.to_device(case.scale)
+    try:
+        args = afb.make_args(px.partial, d_a, d_b, d_s, case.m, case.n, case.k, flags=pkg.FLAG_C_F32)
+        outs = []
+        for _ in range(2):
+            afb.memset(px.c, 0, case.m * case.n * 2)
+            px.gemm_publishing_tiles(args)
+            px.allreduce_tiles()
+            afb.device_sync()
+            outs.append(afb.to_host(px.c, (case.m, case.n), np.uint16))
+        counts = afb.to_host(px.tile_done, (px.num_tiles,), np.uint32)
+        assert afb.read_status()[0] == 0
+        assert np.all(counts == counts[0]) and counts[0] > 0 and counts[0] % 2 == 0      # every tile counted equally, twice
+        assert np.array_equal(outs[0], outs[1])
+        check_close(oracle, oracle.gemm(case, threads=4), outs[0], "tile exchange, one rank")
+    finally:
+        px.close()
+        for p in (d_a, d_b, d_s):
+            afb.free(p)
+
+
 def test_unsupported_requests_return_status_not_fault(afb):
     case = T.make_case(4, 128, 256, layout=0, seed=1)
     dc = T.DeviceCase(afb, case)
@@ -228,8 +265,9 @@ def test_unsupported_requests_return_status_not_fault(afb):
         dc.close()
 
 
-def test_host_pointer_entry_point(afb, oracle):
-    case = T.make_case(64, 256, 512, seed=12)
+@pytest.mark.parametrize("m,n,k", [(64, 256, 512), (48, 4096, 256), (300, 8192, 128)])     # the last two take the chunked, pipelined path
+def test_host_pointer_entry_point(afb, oracle, m, n, k):
+    case = T.make_case(m, n, k, seed=12)
     c = np.zeros((case.m, case.n), np.uint16)
     args = afb.make_args(c, case.a, case.b, case.scale, case.m, case.n, case.k, ldb=case.ldb)
     afb.gemm_host(args)
