@@ -317,6 +317,21 @@ extern "C" int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_d
     return launch_prefill_ts_tiles(*args, ctx, tile_done, (cudaStream_t)stream);
 }
 
+extern "C" int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream) {
+    if (!args || !stage || !args->ptr_a || !args->ptr_b || !args->ptr_scale) return AFB_ERR_BAD_ARG;
+    if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;
+    if (args->lda < args->k || args->ldb < args->k || args->b_layout != AFB_LAYOUT_COL) return AFB_ERR_BAD_ARG;
+    if (!(args->flags & AFB_FLAG_C_F32)) return AFB_ERR_UNSUPPORTED;   // the partial sums travel as fp32
+    if (world == 0 || world > AFB_MAX_RANKS || rank >= world) return AFB_ERR_BAD_ARG;
+    for (uint32_t q = 0; q < world; ++q) if (!stage[q] || (uintptr_t)stage[q] % 16) return AFB_ERR_BAD_ARG;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    afb_gemm_args a = *args;
+    a.ptr_c = stage[rank];   // never written in this mode; keeps the common validation happy
+    a.ldc = a.n;
+    return launch_prefill_ts_push(a, ctx, stage, world, rank, (cudaStream_t)stream);
+}
+
 extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* ta, void* stream) {
     if (!ta) return AFB_ERR_BAD_ARG;
     const afb_allreduce_args* a = &ta->base;

@@ -43,6 +43,10 @@ struct TsParams {
     uint32_t group_m;      // tile order: groups of group_m row tiles; inside a group the channel tiles advance, row tile fastest
     uint32_t c_f32;
     uint32_t* tile_done;   // optional: per-tile counters, +kWorkerWarps when a tile of C has been stored (system-scope release)
+    // optional (row-parallel reduce-scatter fused into the epilogue): fp32 C rows [o*push_rows, (o+1)*push_rows) go to rank o's
+    // staging buffer, slot push_rank, instead of to p.c: push[o] + (push_rank * push_rows + local_row) * ldc + n
+    float* push[AFB_MAX_RANKS];
+    uint32_t push_rows, push_rank, push_on;
     int32_t* status;
 };
 
@@ -288,6 +292,10 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                     const uint32_t mrow = m0 + col;
                     if (p.c_f32) {
                         float* dst = reinterpret_cast<float*>(p.c) + (size_t)mrow * p.ldc + nn;
+                        if (p.push_on) {   // a tile never straddles two owners (push_rows is a multiple of the tile height)
+                            const uint32_t owner = mrow / p.push_rows;
+                            dst = p.push[owner] + ((size_t)p.push_rank * p.push_rows + (mrow - owner * p.push_rows)) * p.ldc + nn;
+                        }
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (mrow + j < p.m) dst[(size_t)j * p.ldc] = __uint_as_float(r[j]) * scale;
@@ -360,7 +368,8 @@ uint32_t pick_group_m(const afb_gemm_args& a, uint32_t m_tiles, uint32_t n_tiles
 }
 
 template <int BITS, bool GROUPED, int BMA>
-int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr) {
+int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr, void* const* push = nullptr,
+                  uint32_t push_world = 0, uint32_t push_rank = 0) {
     using L = TsLayout<BITS, BMA>;
     static_assert(L::kDynamic <= 232448, "shared memory budget");
     CUtensorMap ta, tw;
@@ -380,6 +389,10 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
     p.group_m = tile_done ? p.m_tiles : pick_group_m(a, p.m_tiles, p.n_tiles, BMA, ctx->sm_count);   // the exchange kernel assumes row-tile-fastest order
     p.tile_done = tile_done;
+    p.push_on = push ? 1u : 0u;
+    p.push_rank = push_rank;
+    p.push_rows = push ? a.m / push_world : 0;
+    for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push[q] = (push && q < push_world) ? reinterpret_cast<float*>(push[q]) : nullptr;
     p.status = ctx->status;
     auto kern = prefill_ts_kernel<BITS, GROUPED, BMA>;
     static int attr_dev = -1;  // per template instance
@@ -407,6 +420,14 @@ void prefill_ts_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* ti
 int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* tile_done, cudaStream_t s) {
     if (!prefill_supports(a) || a.group_size != 0 || a.b_bits != 8 || a.m <= 128) return AFB_ERR_UNSUPPORTED;   // the row-parallel path: int8, per-channel
     return launch_ts_cfg<8, false, 256>(a, ctx, s, tile_done);
+}
+
+// Row-parallel GEMM whose epilogue is the reduce-scatter: every tile of fp32 partial sums is stored straight into the staging
+// buffer of the rank that owns those rows (peer stores over NVLink), slot = this rank.
+int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s) {
+    if (!prefill_supports(a) || a.group_size != 0 || a.b_bits != 8 || a.m <= 128) return AFB_ERR_UNSUPPORTED;
+    if (world == 0 || world > AFB_MAX_RANKS || rank >= world || a.m % (world * 256) != 0 || a.ldc != a.n) return AFB_ERR_UNSUPPORTED;
+    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank);
 }
 
 int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {

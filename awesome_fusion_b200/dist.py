@@ -127,6 +127,30 @@ class PeerExchange:
         self.lib.lib.afb_ksplit_allreduce_launch.argtypes = [ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
         self.lib.check(self.lib.lib.afb_ksplit_allreduce_launch(ctypes.byref(a), stream), "afb_ksplit_allreduce_launch")
 
+    def push_supported(self):
+        return self.partial_f32 and self.m % (256 * self.world) == 0
+
+    def gemm_pushing(self, args, stream=None):
+        """The K-split GEMM with the reduce-scatter in its epilogue: each tile of fp32 partial sums is stored into the
+        partial-sum buffer of the rank owning those rows (read there as float[world][m / world][n], slot = this rank)."""
+        from .capi import GemmArgs
+        f = self.lib.lib.afb_gemm_launch_push
+        f.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]
+        stage = (ctypes.c_void_p * MAX_RANKS)(*[self.partials[q] for q in range(self.world)])
+        self.lib.check(f(ctypes.byref(args), stage, self.world, self.rank, stream), "afb_gemm_launch_push")
+
+    def allreduce_pushed(self, stream=None):
+        """Finishes gemm_pushing(): waits for every rank's GEMM, sums this rank's rows from its LOCAL slots in rank order,
+        rounds once and broadcasts the bf16 rows."""
+        self.epoch += 1
+        a = self.args()
+        a.epoch = self.epoch
+        rows = self.m // self.world
+        for q in range(self.world):   # slot q, addressed by absolute row as the kernel does
+            a.partial[q] = self.partial + (q * rows - self.rank * rows) * self.n * 4
+        self.lib.lib.afb_ksplit_allreduce_launch.argtypes = [ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
+        self.lib.check(self.lib.lib.afb_ksplit_allreduce_launch(ctypes.byref(a), stream), "afb_ksplit_allreduce_launch")
+
     def gemm_publishing_tiles(self, args, stream=None):
         """The K-split GEMM into this rank's partial-sum buffer, counting finished tiles for allreduce_tiles()."""
         f = self.lib.lib.afb_gemm_launch_tiles
@@ -166,7 +190,8 @@ def cast_f32_to_bf16(lib, dst, src, rows, cols, stream=None):
 class ShardedMLP:
     """The sharded benchmark step: column-parallel up-projection + row-parallel down-projection (int8, per-channel).
 
-    exchange: "overlap" (tile-granular exchange next to the GEMM) | "fused" (one exchange kernel after the GEMM) | "nccl" |
+    exchange: "push" (reduce-scatter in the GEMM epilogue over peer stores, then a local sum + broadcast kernel) |
+              "overlap" (tile-granular exchange next to the GEMM) | "fused" (one exchange kernel after the GEMM) | "nccl" |
               "auto" (fused when the box shares memory between the processes, else nccl).
     partial:  "f32" (exact, ordered sum) | "bf16" (half the NVLink bytes; each partial rounded once)."""
 
@@ -202,26 +227,33 @@ class ShardedMLP:
         self.tdist = tdist
         mode = exchange
         if mode == "auto":
-            # measured on 8 GPUs: running the exchange next to the GEMM slows the GEMM (both contend for L2 bandwidth) by as
-            # much as the overlap saves (0.853 vs 0.841 ms per step); the single exchange kernel after the GEMM is the default
-            mode = "fused"
+            # measured: the reduce-scatter in the GEMM epilogue beats the exchange kernel after the GEMM, which beats the
+            # tile-granular exchange next to the GEMM (whose own NVLink traffic slows the GEMM by as much as the overlap saves)
+            mode = "push" if (partial == "f32" and m % (256 * world) == 0) else "fused"
         self.overlap = mode == "overlap"
+        self.push = mode == "push"
         if mode == "overlap":
             mode = "fused"
             self.side = torch.cuda.Stream()
+        if mode == "push":
+            if partial != "f32" or m % (256 * world) != 0:
+                raise pkg.AfbError(-4, "the push exchange needs fp32 partial sums and M a multiple of 256 * world", "")
+            mode = "fused"
         if mode == "fused":
             self.px = PeerExchange(lib, tdist, rank, world, m, down_n, partial_f32=(partial == "f32"))
             if not self.px.ok:
                 why = getattr(self.px, "error", "a peer could not share its memory")
                 self.px.close(); self.px = None
                 self.overlap = False
-                if exchange in ("fused", "overlap"):
+                self.push = False
+                if exchange in ("fused", "overlap", "push"):
                     raise pkg.AfbError(-3, "peer-memory exchange unavailable", why)
                 if rank == 0:
                     print(f"peer memory unavailable ({why}); using the NCCL exchange", flush=True)
                 mode = "nccl"
         if mode == "fused":
             self.exchange_name = (f"tile-granular peer-memory all-reduce overlapped with the GEMM ({partial} partial sums)" if self.overlap
+                                  else "reduce-scatter in the GEMM epilogue (peer stores of fp32 tiles) + local sum and bf16 broadcast" if self.push
                                   else f"fused peer-memory all-reduce after the GEMM ({partial} partial sums)")
             flags = 0 if partial == "bf16" else pkg.FLAG_C_F32
             self.args_down = lib.make_args(self.px.partial, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local, flags=flags)
@@ -248,6 +280,12 @@ class ShardedMLP:
                 self.px.allreduce_tiles(self.side.cuda_stream)
                 done = self.side.record_event()
             torch.cuda.current_stream().wait_event(done)   # the step ends when C is complete on this rank
+            if events:
+                events[2].record()
+            return
+        if self.world > 1 and self.px is not None and self.push:
+            self.px.gemm_pushing(self.args_down, stream)
+            self.px.allreduce_pushed(stream)
             if events:
                 events[2].record()
             return

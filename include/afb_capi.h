@@ -179,6 +179,13 @@ typedef struct afb_tile_allreduce_args {
 int afb_ksplit_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* num_tiles, uint32_t* arrivals);
 int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_done, void* stream);
 int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* args, void* stream);
+/* Reduce-scatter fused into the GEMM epilogue: the prefill GEMM (int8, per-channel scales, M a multiple of 256 * world) stores
+ * every tile of its fp32 partial sums straight into the staging buffer of the rank that owns those rows, over NVLink:
+ * stage[o] is rank o's float[world][M / world][N] buffer (mapped in this process), and this rank fills slot `rank` of each.
+ * args->ptr_c is ignored.  Follow it, on the same stream, with afb_ksplit_allreduce_launch whose partial[q] point at the
+ * LOCAL slots (partial[q] = own_stage + (q * (M/world) - rank * (M/world)) * N floats, ld_partial = N): its first phase then
+ * waits for every rank's GEMM, its sum reads local memory only, and its second phase broadcasts the bf16 rows. */
+int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream);
 /* fp32 [rows, cols] (ld_src) -> bf16 (ld_dst), round to nearest even: finishes a K-split whose partial
  * sums were combined by a library collective instead of afb_ksplit_allreduce_launch. */
 int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uint32_t cols, uint32_t ld_dst, uint32_t ld_src, void* stream);

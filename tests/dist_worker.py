@@ -141,6 +141,37 @@ def main():
     if rank == 0:
         print(f"tile-granular: max rel err {mx:.3e} nrms {nrms:.3e}", flush=True)
     px.close()
+    # reduce-scatter in the GEMM epilogue (peer stores) + local sum and broadcast: the same bits as GEMM + fused exchange
+    mp = 256 * world
+    case_p = T.make_case(mp, n, k, seed=34)
+    ref_p = oracle.gemm(case_p, threads=4)
+    shard_p = sub_case(case_p, k_rng=(k_lo, k_hi))
+    p_a, p_b, p_s = lib.to_device(shard_p.a), lib.to_device(shard_p.b), lib.to_device(shard_p.scale)
+    px = D.PeerExchange(lib, tdist, rank, world, mp, n, partial_f32=True)
+    assert px.ok and px.push_supported()
+    args = lib.make_args(px.partial, p_a, p_b, p_s, mp, n, shard_p.k, flags=pkg.FLAG_C_F32)
+    outs = []
+    for step in range(4):
+        lib.memset(px.c, 0, mp * n * 2)
+        tdist.barrier(); torch.cuda.synchronize()
+        if step == 0:
+            lib.gemm_launch(args, stream)
+            px.allreduce(stream)
+        else:
+            px.gemm_pushing(args, stream)
+            px.allreduce_pushed(stream)
+        torch.cuda.synchronize()
+        outs.append(lib.to_host(px.c, (mp, n), np.uint16))
+    st = lib.read_status()
+    assert st[0] == 0, f"device status {st}"
+    assert all(np.array_equal(outs[0], o) for o in outs[1:]), "epilogue reduce-scatter differs from GEMM + fused exchange"
+    mx, nrms, _ = oracle.compare(ref_p, outs[1], T.rms(ref_p) * 0.05)
+    assert mx <= 1e-2, f"epilogue reduce-scatter: max rel err {mx}"
+    if rank == 0:
+        print(f"push: max rel err {mx:.3e} nrms {nrms:.3e}", flush=True)
+    px.close()
+    for p in (p_a, p_b, p_s):
+        lib.free(p)
     # NCCL comparison path
     p32 = torch.empty((m, n), device="cuda", dtype=torch.float32)
     c16 = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
