@@ -1,7 +1,8 @@
 // Row-parallel (K-split) exchange: the all-reduce of per-GPU partial sums as one kernel per GPU over
 // NVLink peer memory (reduce-scatter by peer loads, all-gather by peer stores), plus the fp32 -> bf16
 // cast that finishes the NCCL comparison path.  The reference is single-GPU (bfAintBGemm.cc:63) and has
-// no counterpart.  Only plain ld/st reach peer memory: no TMA, no multicast.
+// no counterpart.  Only plain ld/st reach peer memory (no TMA); the broadcast of the result rows may instead be ONE
+// multimem.st per 16 bytes to an NVSwitch multicast address, when the caller has one.
 //
 // Signals: every rank owns uint32 signals[2][AFB_MAX_RANKS]; rank q writes `epoch` into
 // signals[phase][q] of every rank.  Phase 0: "my partial of this epoch is complete" (the GEMM that
@@ -19,6 +20,7 @@ constexpr int kThreads = 512;
 struct ARParams {
     const void* partial[AFB_MAX_RANKS];
     uint16_t* c[AFB_MAX_RANKS];
+    uint16_t* c_multicast;   // optional: one address that the NVSwitch replicates into every rank's C
     uint32_t* signals[AFB_MAX_RANKS];
     uint32_t rank, world, m, n, ld_partial, ldc, partial_f32, epoch;
     unsigned long long wait_ns;
@@ -52,6 +54,11 @@ __device__ bool wait_all(const uint32_t* my_signals, int phase, uint32_t world, 
     return true;
 }
 
+// One 16-byte store to a multicast address: the switch writes it into every rank's copy of the buffer.
+__device__ __forceinline__ void st16_multicast(void* p, const uint4& v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+                 "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
 __device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
@@ -110,9 +117,13 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
                     }
             }
             const uint4 out = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+            if (p.c_multicast) {
+                st16_multicast(p.c_multicast + (size_t)row * p.ldc + col, out);   // leaves this GPU once, lands in all C
+            } else {
 #pragma unroll
-            for (int q = 0; q < AFB_MAX_RANKS; ++q)
-                if (q < (int)p.world) *reinterpret_cast<uint4*>(p.c[q] + (size_t)row * p.ldc + col) = out;
+                for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                    if (q < (int)p.world) *reinterpret_cast<uint4*>(p.c[q] + (size_t)row * p.ldc + col) = out;
+            }
         }
     }
     // the last CTA to finish tells every rank that this rank's block is in place, then waits for theirs
@@ -261,6 +272,7 @@ extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* st
         if (!a->partial[q] || !a->c[q] || !a->signals[q]) return AFB_ERR_BAD_ARG;
         if ((uintptr_t)a->partial[q] % 16 || (uintptr_t)a->c[q] % 16) return AFB_ERR_BAD_ARG;
     }
+    if ((uintptr_t)a->c_multicast % 16) return AFB_ERR_BAD_ARG;
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;
     if (!g_cta_done[ctx->device]) {
@@ -277,6 +289,7 @@ extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* st
     }
     p.rank = a->rank; p.world = a->world; p.m = a->m; p.n = a->n; p.ld_partial = a->ld_partial; p.ldc = a->ldc;
     p.partial_f32 = a->partial_f32; p.epoch = a->epoch;
+    p.c_multicast = reinterpret_cast<uint16_t*>(a->c_multicast);
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
     p.cta_done = g_cta_done[ctx->device];
     p.status = ctx->status;
@@ -363,6 +376,7 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
     }
     p.rank = a->rank; p.world = a->world; p.m = a->m; p.n = a->n; p.ld_partial = a->ld_partial; p.ldc = a->ldc;
     p.partial_f32 = 1; p.epoch = a->epoch;
+    p.c_multicast = nullptr;   // the tile-granular form stores to each peer
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
     p.cta_done = g_cta_done_tile[ctx->device];
     p.status = ctx->status;

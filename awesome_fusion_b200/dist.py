@@ -13,6 +13,7 @@ The partition arithmetic (`split_range`, `column_shard`, `k_shard`) is plain Pyt
 tested on CPU ranks.
 """
 import ctypes
+import os
 
 MAX_RANKS = 8
 
@@ -46,7 +47,7 @@ class AllReduceArgs(ctypes.Structure):
     _fields_ = [("partial", ctypes.c_void_p * MAX_RANKS), ("c", ctypes.c_void_p * MAX_RANKS), ("signals", ctypes.c_void_p * MAX_RANKS),
                 ("rank", ctypes.c_uint32), ("world", ctypes.c_uint32), ("m", ctypes.c_uint32), ("n", ctypes.c_uint32),
                 ("ld_partial", ctypes.c_uint32), ("ldc", ctypes.c_uint32), ("partial_f32", ctypes.c_uint32), ("epoch", ctypes.c_uint32),
-                ("wait_ms", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+                ("wait_ms", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("c_multicast", ctypes.c_void_p)]
 
 
 class TileAllReduceArgs(ctypes.Structure):
@@ -60,15 +61,23 @@ class PeerExchange:
     Each rank allocates (through the C ABI, so the allocation is a whole cudaMalloc block) its partial-sum
     buffer, its result buffer C and its signal words, exports the three handles, and maps every peer's."""
 
-    def __init__(self, lib, torch_dist, rank, world, m, n, partial_f32=True, wait_ms=2000):
+    def __init__(self, lib, torch_dist, rank, world, m, n, partial_f32=True, wait_ms=2000, multicast=None):
         self.lib, self.rank, self.world, self.m, self.n = lib, rank, world, m, n
+        if multicast is None:
+            multicast = os.environ.get("AFB_EXCHANGE_MULTICAST", "1") != "0"
+        self.c_multicast = None   # NVSwitch multicast address of C, when torch's symmetric memory provides one
+        self._symm = None
         self.partial_f32 = partial_f32
         self.wait_ms = wait_ms
         self.epoch = 0        # exchanges issued (orders the signal words)
         self.tile_epoch = 0   # tile-publishing GEMMs issued (orders the per-tile counters)
         pbytes = m * n * (4 if partial_f32 else 2)
         self.partial = lib.malloc(pbytes)
-        self.c = lib.malloc(m * n * 2)
+        self.c = None
+        if world > 1 and multicast:
+            self._symmetric_c(torch_dist, m * n * 2)
+        if self.c is None:
+            self.c = lib.malloc(m * n * 2)
         self.signals = lib.malloc(2 * MAX_RANKS * 4)
         lib.memset(self.signals, 0, 2 * MAX_RANKS * 4)
         # per-tile completion counters of the tile-granular form (fp32 partial sums only)
@@ -87,7 +96,8 @@ class PeerExchange:
         # No rank may raise between the collectives below (the others would wait for it for ever):
         # failures are recorded, exchanged, and every rank reaches the same verdict.
         try:
-            mine = (lib.ipc_export(self.partial), lib.ipc_export(self.c), lib.ipc_export(self.signals), lib.ipc_export(self.tile_done))
+            mine = (lib.ipc_export(self.partial), None if self._symm else lib.ipc_export(self.c), lib.ipc_export(self.signals),
+                    lib.ipc_export(self.tile_done))
         except Exception as e:  # noqa: BLE001
             mine, self.error = None, str(e)
         everyone = [None] * world
@@ -102,6 +112,9 @@ class PeerExchange:
                     else:
                         ptrs = []
                         for h in handles:
+                            if h is None:   # C lives in symmetric memory: mapped by its rendezvous
+                                ptrs.append(int(self._symm[1].buffer_ptrs[q]))
+                                continue
                             ptrs.append(lib.ipc_import(h))
                             self._imported.append(ptrs[-1])
                         self.partials[q], self.cs[q], self.sigs[q], self.tds[q] = ptrs
@@ -111,6 +124,33 @@ class PeerExchange:
         torch_dist.all_gather_object(verdicts, self.ok)
         self.ok = all(verdicts)
 
+    def _symmetric_c(self, torch_dist, nbytes):
+        """Allocates C in torch's symmetric memory so that the NVSwitch can replicate the result rows (multimem.st).
+        Every step is agreed on by all ranks before the next collective one; on any failure C falls back to a plain buffer."""
+        import torch
+        t = None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(nbytes // 2, dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+        except Exception:  # noqa: BLE001
+            t = None
+        oks = [None] * self.world
+        torch_dist.all_gather_object(oks, t is not None)
+        if not all(oks):
+            return
+        hdl, mc = None, 0
+        try:
+            hdl = symm.rendezvous(t, torch_dist.group.WORLD)
+            mc = int(hdl.multicast_ptr or 0)
+        except Exception:  # noqa: BLE001
+            hdl, mc = None, 0
+        torch_dist.all_gather_object(oks, hdl is not None and mc != 0)
+        if not all(oks):
+            return
+        self._symm = (t, hdl)
+        self.c = int(t.data_ptr())
+        self.c_multicast = mc
+
     def args(self):
         a = AllReduceArgs()
         for q in range(self.world):
@@ -118,6 +158,7 @@ class PeerExchange:
         a.rank, a.world, a.m, a.n = self.rank, self.world, self.m, self.n
         a.ld_partial, a.ldc, a.partial_f32 = self.n, self.n, 1 if self.partial_f32 else 0
         a.wait_ms, a.reserved = self.wait_ms, 0
+        a.c_multicast = self.c_multicast
         return a
 
     def allreduce(self, stream=None):
@@ -177,8 +218,10 @@ class PeerExchange:
         self.lib.device_sync()
         for p in self._imported:
             self.lib.ipc_release(p)
-        for p in (self.partial, self.c, self.signals, self.tile_done):
-            self.lib.free(p)
+        for p in (self.partial, None if self._symm else self.c, self.signals, self.tile_done):
+            if p is not None:
+                self.lib.free(p)
+        self._symm = None
 
 
 def cast_f32_to_bf16(lib, dst, src, rows, cols, stream=None):
@@ -255,6 +298,8 @@ class ShardedMLP:
             self.exchange_name = (f"tile-granular peer-memory all-reduce overlapped with the GEMM ({partial} partial sums)" if self.overlap
                                   else "reduce-scatter in the GEMM epilogue (peer stores of fp32 tiles) + local sum and bf16 broadcast" if self.push
                                   else f"fused peer-memory all-reduce after the GEMM ({partial} partial sums)")
+            if self.px.c_multicast and not self.overlap:
+                self.exchange_name += "; result rows broadcast by multimem.st through the NVSwitch"
             flags = 0 if partial == "bf16" else pkg.FLAG_C_F32
             self.args_down = lib.make_args(self.px.partial, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local, flags=flags)
         else:

@@ -143,7 +143,7 @@ int afb_ipc_import(const unsigned char handle[AFB_IPC_HANDLE_BYTES], void** dev_
 int afb_ipc_release(void* dev_ptr);
 
 /* All-reduce of the K-split partial sums as ONE kernel per GPU over peer memory (plain peer
- * loads/stores through NVLink; no multicast): rank r waits until every rank's partial is complete,
+ * loads/stores through NVLink; the broadcast of the result may use an NVSwitch multicast store): rank r waits until every rank's partial is complete,
  * sums rows block r of all `world` partials in rank order (fp32), rounds to bf16 and stores the
  * result into every rank's C, then waits until every rank has stored its block here.  When the
  * kernel ends on a rank, that rank's C holds the complete sum and no peer reads its partial any more.
@@ -161,6 +161,9 @@ typedef struct afb_allreduce_args {
     uint32_t  epoch;
     uint32_t  wait_ms;                /* bound of each wait in milliseconds (0 = 2000) */
     uint32_t  reserved;
+    void*     c_multicast;            /* optional (NULL = unused): an NVLink multicast address bound to the same bytes as every
+                                       * c[q] (same offset in all of them).  The result rows then leave this GPU once, as
+                                       * multimem.st, and the switch writes them into every rank's C; c[] is not written. */
 } afb_allreduce_args;
 int afb_ksplit_allreduce_launch(const afb_allreduce_args* args, void* stream);
 /* Tile-granular form of the same exchange, fused with the K-split GEMM: afb_gemm_launch_tiles is the prefill GEMM

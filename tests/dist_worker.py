@@ -84,8 +84,11 @@ def main():
     k_lo, k_hi = D.k_shard(k, world, rank)
     shard = sub_case(case, k_rng=(k_lo, k_hi))
     d_a, d_b, d_s = lib.to_device(shard.a), lib.to_device(shard.b), lib.to_device(shard.scale)
-    for partial in ("f32", "bf16"):
-        px = D.PeerExchange(lib, tdist, rank, world, m, n, partial_f32=(partial == "f32"))
+    first_f32 = None
+    for partial, multicast in (("f32", True), ("f32", False), ("bf16", True)):
+        # multicast=True: C in symmetric memory, result rows broadcast by multimem.st where the box offers it (else plain stores)
+        px = D.PeerExchange(lib, tdist, rank, world, m, n, partial_f32=(partial == "f32"), multicast=multicast)
+        assert multicast or px.c_multicast is None
         assert px.ok, getattr(px, "error", "peer exchange setup failed")
         args = lib.make_args(px.partial, d_a, d_b, d_s, m, n, shard.k, flags=pkg.FLAG_C_F32 if partial == "f32" else 0)
         outs = []
@@ -109,8 +112,12 @@ def main():
         lo, hi = t.clone(), t.clone()
         tdist.all_reduce(lo, op=tdist.ReduceOp.MIN); tdist.all_reduce(hi, op=tdist.ReduceOp.MAX)
         assert torch.equal(lo, hi), "ranks disagree on the all-reduced result"
+        if partial == "f32":
+            if first_f32 is None:
+                first_f32 = outs[0]
+            assert np.array_equal(first_f32, outs[0]), "multicast and plain broadcast disagree"
         if rank == 0:
-            print(f"fused {partial}: max rel err {mx:.3e} nrms {nrms:.3e}", flush=True)
+            print(f"fused {partial} (multicast address: {'yes' if px.c_multicast else 'no'}): max rel err {mx:.3e} nrms {nrms:.3e}", flush=True)
         px.close()
     # tile-granular form: GEMM publishing tiles + exchange kernel on a second stream (needs M > 128: same shape, M = 256)
     px = D.PeerExchange(lib, tdist, rank, world, m, n, partial_f32=True)

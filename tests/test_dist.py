@@ -47,3 +47,4 @@ def test_sharding_on_two_gpus():
         pytest.skip("needs two GPUs in the box")
     res = _launch("gpu", 2, 600)
     assert res.returncode == 0 and "DIST-OK gpu" in res.stdout, res.stdout[-4000:]
+    print("\n".join(l for l in res.stdout.splitlines() if "max rel err" in l))
