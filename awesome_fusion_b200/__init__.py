@@ -10,7 +10,7 @@ from .capi import (  # noqa: F401
     GemmArgs,
     Library,
     ENC_TWOS, ENC_OFFSET, LAYOUT_ROW, LAYOUT_COL, SCALE_F32, SCALE_BF16,
-    VARIANT_AUTO, VARIANT_DECODE, VARIANT_PREFILL, VARIANT_NAIVE, FLAG_C_F32, FLAG_PREFILL_SMEM_B, FLAG_PREFILL_TMEM_A,
+    VARIANT_AUTO, VARIANT_DECODE, VARIANT_PREFILL, VARIANT_NAIVE, FLAG_C_F32, FLAG_PREFILL_SMEM_B, FLAG_PREFILL_TMEM_A, FLAG_PUSH_VIA_LOCAL,
     library_path, load,
 )
 from .build import build_library  # noqa: F401
@@ -18,5 +18,5 @@ from .build import build_library  # noqa: F401
 __all__ = [
     "AfbError", "GemmArgs", "Library", "library_path", "load", "build_library",
     "ENC_TWOS", "ENC_OFFSET", "LAYOUT_ROW", "LAYOUT_COL", "SCALE_F32", "SCALE_BF16",
-    "VARIANT_AUTO", "VARIANT_DECODE", "VARIANT_PREFILL", "VARIANT_NAIVE", "FLAG_C_F32", "FLAG_PREFILL_SMEM_B", "FLAG_PREFILL_TMEM_A",
+    "VARIANT_AUTO", "VARIANT_DECODE", "VARIANT_PREFILL", "VARIANT_NAIVE", "FLAG_C_F32", "FLAG_PREFILL_SMEM_B", "FLAG_PREFILL_TMEM_A", "FLAG_PUSH_VIA_LOCAL",
 ]

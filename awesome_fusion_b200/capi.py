@@ -16,6 +16,7 @@ VARIANT_AUTO, VARIANT_DECODE, VARIANT_PREFILL, VARIANT_NAIVE = 0, 1, 2, 3
 FLAG_C_F32 = 1
 FLAG_PREFILL_SMEM_B = 2
 FLAG_PREFILL_TMEM_A = 4
+FLAG_PUSH_VIA_LOCAL = 8
 IPC_HANDLE_BYTES = 64
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

@@ -340,8 +340,12 @@ extern "C" int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;
     afb_gemm_args a = *args;
-    a.ptr_c = stage[rank];   // never written in this mode; keeps the common validation happy
-    a.ldc = a.n;
+    if (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) {
+        if (!a.ptr_c || (uintptr_t)a.ptr_c % 16 || a.ldc != a.n || a.n % 4) return AFB_ERR_BAD_ARG;   // local fp32 [M,N] scratch
+    } else {
+        a.ptr_c = stage[rank];   // never written in this mode; keeps the common validation happy
+        a.ldc = a.n;
+    }
     return launch_prefill_ts_push(a, ctx, stage, world, rank, (cudaStream_t)stream);
 }
 

@@ -33,6 +33,8 @@ constexpr int kWorkerWarps = 8;   // measured: 8 beats 16 (1.10 vs 1.04 PFLOP/s 
 constexpr int kKParts = kWorkerWarps / 4;            // warps per TMEM lane quarter = parts the 64-wide K step is cut into
 constexpr int kKPer = BK / kKParts;                  // k per converter thread and stage (32 or 16)
 constexpr int kThreads = 32 * (2 + kWorkerWarps);   // 320
+constexpr int kFwdWarps = 2;      // optional extra warps that forward finished fp32 tiles to their owner rank
+constexpr int kThreadsFwd = kThreads + 32 * kFwdWarps;
 
 struct TsParams {
     uint16_t* c;
@@ -46,7 +48,9 @@ struct TsParams {
     // optional (row-parallel reduce-scatter fused into the epilogue): fp32 C rows [o*push_rows, (o+1)*push_rows) go to rank o's
     // staging buffer, slot push_rank, instead of to p.c: push[o] + (push_rank * push_rows + local_row) * ldc + n
     float* push[AFB_MAX_RANKS];
-    uint32_t push_rows, push_rank, push_on;
+    uint32_t push_rows, push_rank;
+    uint32_t push_on;      // 0: off; 1: the epilogue stores to the owner directly; 2: the epilogue stores to p.c (local) and the
+                           // forwarder warps copy each finished tile to its owner while the next tile is being computed
     int32_t* status;
 };
 
@@ -59,7 +63,7 @@ struct TsLayout {
     static constexpr int kOffAct = 0;
     static constexpr int kOffRaw = kStages * kActBytes;
     static constexpr int kOffBars = kOffRaw + kStages * kRawBytes;
-    static constexpr int kNumBars = 3 * kStages + 2 * kSlotsA + 2;
+    static constexpr int kNumBars = 3 * kStages + 2 * kSlotsA + 4;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kDynamic = kOffMisc + 16 + 1024;
     static constexpr uint32_t kTmemCols = 512;                   // accumulator [0, BMA) + weight slots [256, 256 + kSlotsA * 32)
@@ -93,7 +97,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 }
 
 template <int BITS, bool GROUPED, int BMA>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsFwd, 1)
 prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w, const TsParams p) {
     using L = TsLayout<BITS, BMA>;
     constexpr int S = L::kStages;
@@ -109,6 +113,8 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
     auto bar_empty_a   = [&](int s) { return bar_base + 8u * (3 * S + kSlotsA + s); };   // MMA done with TMEM slot s
     const uint32_t bar_acc_full = bar_base + 8u * (3 * S + 2 * kSlotsA);
     const uint32_t bar_acc_empty = bar_acc_full + 8u;
+    const uint32_t bar_tile_stored = bar_acc_full + 16u;   // forward mode: the epilogue has stored a tile to local memory
+    const uint32_t bar_tile_fwd = bar_acc_full + 24u;      // forward mode: the forwarder warps have copied it out
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kOffMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -121,6 +127,8 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         for (int s = 0; s < kSlotsA; ++s) { ptx::mbar_init(bar_full_a(s), kWorkerWarps); ptx::mbar_init(bar_empty_a(s), 1); }
         ptx::mbar_init(bar_acc_full, 1);
         ptx::mbar_init(bar_acc_empty, kWorkerWarps);
+        ptx::mbar_init(bar_tile_stored, kWorkerWarps);
+        ptx::mbar_init(bar_tile_fwd, kFwdWarps);
         *abort_flag = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmap_act);
@@ -192,7 +200,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 if (ok) ptx::umma_commit(bar_acc_full);
             }
         }
-    } else {
+    } else if (warp < 2 + kWorkerWarps) {
         // ======================= converters + epilogue =======================
         const uint32_t q = (uint32_t)(warp & 3);             // TMEM lane quarter this warp may touch
         const uint32_t kq = (uint32_t)(warp - 2) >> 2;        // which part of the 64-wide K step / which part of the columns
@@ -281,6 +289,10 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             if (!GROUPED && nn < p.n)
                 scale = p.scale_dtype == AFB_SCALE_BF16 ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(p.scale)[nn] << 16)
                                                        : reinterpret_cast<const float*>(p.scale)[nn];
+            if (p.push_on == 2 && !wait_or_abort(bar_tile_fwd, (it & 1u) ^ 1u, abort_flag)) {   // the previous tile has left
+                if (!*abort_flag) { report_timeout(p.status, 26, (int)t, -1); *abort_flag = 1; }
+                break;
+            }
             constexpr int kColsPerWarp = BMA / kKParts;   // the warps of a lane quarter split the activation rows
 #pragma unroll 1
             for (int c0 = 0; c0 < kColsPerWarp; c0 += 32) {
@@ -292,7 +304,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                     const uint32_t mrow = m0 + col;
                     if (p.c_f32) {
                         float* dst = reinterpret_cast<float*>(p.c) + (size_t)mrow * p.ldc + nn;
-                        if (p.push_on) {   // a tile never straddles two owners (push_rows is a multiple of the tile height)
+                        if (p.push_on == 1) {   // a tile never straddles two owners (push_rows is a multiple of the tile height)
                             const uint32_t owner = mrow / p.push_rows;
                             dst = p.push[owner] + ((size_t)p.push_rank * p.push_rows + (mrow - owner * p.push_rows)) * p.ldc + nn;
                         }
@@ -309,11 +321,46 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             }
             ptx::tc_fence_before_sync();
             if (p.tile_done) __threadfence_system();   // this lane's stores of the tile are visible to every GPU before the count below
+            if (p.push_on == 2) __threadfence();       // ... and to the forwarder warps, which read them back through L2
             __syncwarp();
             if (lane == 0) {
                 ptx::mbar_arrive(bar_acc_empty);
+                if (p.push_on == 2) ptx::mbar_arrive(bar_tile_stored);
                 if (p.tile_done) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.tile_done + t), "r"(1u) : "memory");
             }
+        }
+    }
+
+    else if (p.push_on == 2) {
+        // ======================= forwarders (only launched in forward mode) =======================
+        // Copy each finished 256 x 128 fp32 tile from local memory to the staging buffer of the rank owning its rows: 512
+        // contiguous bytes per warp instruction, issued while the rest of the CTA computes the next tile.
+        const uint32_t fw = (uint32_t)(warp - (2 + kWorkerWarps));
+        uint32_t it = 0;
+        for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            if (!wait_or_abort(bar_tile_stored, it & 1u, abort_flag)) {
+                if (!*abort_flag) { report_timeout(p.status, 27, (int)t, -1); *abort_flag = 1; }
+                break;
+            }
+            uint32_t mt_, nt_;
+            tile_coords(p, t, mt_, nt_);
+            const uint32_t m0 = mt_ * BMA, n0 = nt_ * BNW;
+            const uint32_t owner = m0 / p.push_rows;
+            const float* src = reinterpret_cast<const float*>(p.c) + (size_t)m0 * p.ldc + n0 + lane * 4;
+            float* dst = p.push[owner] + ((size_t)p.push_rank * p.push_rows + (m0 - owner * p.push_rows)) * p.ldc + n0 + lane * 4;
+            const bool col_ok = n0 + lane * 4 < p.n;
+            constexpr int kBatch = 8;
+            for (uint32_t r0 = fw * kBatch; r0 < (uint32_t)BMA; r0 += kFwdWarps * kBatch) {
+                float4 v[kBatch];
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j)
+                    if (col_ok && m0 + r0 + j < p.m) v[j] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(r0 + j) * p.ldc));
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j)
+                    if (col_ok && m0 + r0 + j < p.m) *reinterpret_cast<float4*>(dst + (size_t)(r0 + j) * p.ldc) = v[j];
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tile_fwd);
         }
     }
 
@@ -369,7 +416,7 @@ uint32_t pick_group_m(const afb_gemm_args& a, uint32_t m_tiles, uint32_t n_tiles
 
 template <int BITS, bool GROUPED, int BMA>
 int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr, void* const* push = nullptr,
-                  uint32_t push_world = 0, uint32_t push_rank = 0) {
+                  uint32_t push_world = 0, uint32_t push_rank = 0, bool push_via_local = false) {
     using L = TsLayout<BITS, BMA>;
     static_assert(L::kDynamic <= 232448, "shared memory budget");
     CUtensorMap ta, tw;
@@ -389,7 +436,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
     p.group_m = tile_done ? p.m_tiles : pick_group_m(a, p.m_tiles, p.n_tiles, BMA, ctx->sm_count);   // the exchange kernel assumes row-tile-fastest order
     p.tile_done = tile_done;
-    p.push_on = push ? 1u : 0u;
+    p.push_on = push ? (push_via_local ? 2u : 1u) : 0u;
     p.push_rank = push_rank;
     p.push_rows = push ? a.m / push_world : 0;
     for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push[q] = (push && q < push_world) ? reinterpret_cast<float*>(push[q]) : nullptr;
@@ -403,7 +450,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
-    kern<<<grid, kThreads, L::kDynamic, s>>>(ta, tw, p);
+    kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);
@@ -427,7 +474,7 @@ int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* ti
 int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s) {
     if (!prefill_supports(a) || a.group_size != 0 || a.b_bits != 8 || a.m <= 128) return AFB_ERR_UNSUPPORTED;
     if (world == 0 || world > AFB_MAX_RANKS || rank >= world || a.m % (world * 256) != 0 || a.ldc != a.n) return AFB_ERR_UNSUPPORTED;
-    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank);
+    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank, (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) != 0);
 }
 
 int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {

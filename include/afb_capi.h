@@ -50,6 +50,8 @@ extern "C" {
 #define AFB_FLAG_C_F32 1u /* C is fp32 [M,N] instead of bf16: prefill variant (partial sums of a K-split) and naive variant */
 #define AFB_FLAG_PREFILL_SMEM_B 2u /* prefill variant: force the form that stages the converted weights in shared memory */
 #define AFB_FLAG_PREFILL_TMEM_A 4u /* prefill variant: force the form that keeps the converted weights in tensor memory  */
+#define AFB_FLAG_PUSH_VIA_LOCAL 8u /* afb_gemm_launch_push only: ptr_c is a local fp32 [M,N] scratch (ldc = N); the epilogue stores there and two
+                                      extra warps per CTA forward each finished tile to its owner while the next tile is computed */
 
 /*
  * Kernel argument block.  The first ten fields are the reference's packed kernarg
@@ -185,7 +187,7 @@ int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* args, void* 
 /* Reduce-scatter fused into the GEMM epilogue: the prefill GEMM (int8, per-channel scales, M a multiple of 256 * world) stores
  * every tile of its fp32 partial sums straight into the staging buffer of the rank that owns those rows, over NVLink:
  * stage[o] is rank o's float[world][M / world][N] buffer (mapped in this process), and this rank fills slot `rank` of each.
- * args->ptr_c is ignored.  Follow it, on the same stream, with afb_ksplit_allreduce_launch whose partial[q] point at the
+ * args->ptr_c is ignored unless AFB_FLAG_PUSH_VIA_LOCAL is set.  Follow it, on the same stream, with afb_ksplit_allreduce_launch whose partial[q] point at the
  * LOCAL slots (partial[q] = own_stage + (q * (M/world) - rank * (M/world)) * N floats, ld_partial = N): its first phase then
  * waits for every rank's GEMM, its sum reads local memory only, and its second phase broadcasts the bf16 rows. */
 int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream);

@@ -157,15 +157,17 @@ def main():
     px = D.PeerExchange(lib, tdist, rank, world, mp, n, partial_f32=True)
     assert px.ok and px.push_supported()
     args = lib.make_args(px.partial, p_a, p_b, p_s, mp, n, shard_p.k, flags=pkg.FLAG_C_F32)
+    scratch = lib.malloc(mp * n * 4)   # forward mode: the epilogue stores here, two extra warps per CTA copy the tiles out
+    args_fwd = lib.make_args(scratch, p_a, p_b, p_s, mp, n, shard_p.k, flags=pkg.FLAG_C_F32 | pkg.FLAG_PUSH_VIA_LOCAL)
     outs = []
-    for step in range(4):
+    for step in range(6):
         lib.memset(px.c, 0, mp * n * 2)
         tdist.barrier(); torch.cuda.synchronize()
         if step == 0:
             lib.gemm_launch(args, stream)
             px.allreduce(stream)
         else:
-            px.gemm_pushing(args, stream)
+            px.gemm_pushing(args if step < 4 else args_fwd, stream)
             px.allreduce_pushed(stream)
         torch.cuda.synchronize()
         outs.append(lib.to_host(px.c, (mp, n), np.uint16))
@@ -177,7 +179,7 @@ def main():
     if rank == 0:
         print(f"push: max rel err {mx:.3e} nrms {nrms:.3e}", flush=True)
     px.close()
-    for p in (p_a, p_b, p_s):
+    for p in (p_a, p_b, p_s, scratch):
         lib.free(p)
     # NCCL comparison path
     p32 = torch.empty((m, n), device="cuda", dtype=torch.float32)
