@@ -55,6 +55,13 @@ class TileAllReduceArgs(ctypes.Structure):
     _fields_ = [("base", AllReduceArgs), ("tile_done", ctypes.c_void_p * MAX_RANKS), ("tile_epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
+def push_slot_offset(q, rank, world, m, n):
+    """Byte offset, from the start of rank `rank`'s staging buffer float[world][m / world][n], of the address that the exchange
+    kernel must be given as partial[q] so that its absolute-row indexing (rows rank*m/world .. of an [m, n] matrix) lands in slot q."""
+    rows = m // world
+    return (q * rows - rank * rows) * n * 4
+
+
 class PeerExchange:
     """Buffers of the fused K-split all-reduce, shared between the ranks of one box by CUDA IPC.
 
@@ -186,9 +193,8 @@ class PeerExchange:
         self.epoch += 1
         a = self.args()
         a.epoch = self.epoch
-        rows = self.m // self.world
         for q in range(self.world):   # slot q, addressed by absolute row as the kernel does
-            a.partial[q] = self.partial + (q * rows - self.rank * rows) * self.n * 4
+            a.partial[q] = self.partial + push_slot_offset(q, self.rank, self.world, self.m, self.n)
         self.lib.lib.afb_ksplit_allreduce_launch.argtypes = [ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
         self.lib.check(self.lib.lib.afb_ksplit_allreduce_launch(ctypes.byref(a), stream), "afb_ksplit_allreduce_launch")
 
@@ -351,6 +357,14 @@ class ShardedMLP:
                 cast_f32_to_bf16(lib, self.c_down.data_ptr(), self.partial32.data_ptr(), self.m, self.down_n, stream)
         if events:
             events[2].record()
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's.  Collective in effect: every rank calls it between steps, with
+        none of its kernels in flight, before the process group is destroyed."""
+        self.torch.cuda.synchronize()
+        if self.px is not None:
+            self.px.close()
+            self.px = None
 
     def result_down(self):
         """bf16 result of the down-projection as a torch tensor on the host (tests)."""

@@ -352,6 +352,7 @@ def run_ours(args):
     e2e_obj = {"value": total_flops / e2e["ms"] / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d"] * world,
                "d2h_bytes_per_step": e2e["d2h"] * world, "ms_per_step": e2e["ms"], "api": "afb_gemm_host (C ABI, pinned host buffers)"}
 
+    shutdown(mlp, world, torch)
     if rank != 0:
         return 0
     # roofline of the dominant kernel (the prefill kernel of the up-projection: no exchange inside its events)
@@ -383,6 +384,18 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}
     print(json.dumps(line))
     return 0
+
+
+def shutdown(mlp, world, torch):
+    """Orderly end of a multi-process run: all exchanges done, peer mappings released, then the process group."""
+    if world == 1:
+        return
+    import torch.distributed as tdist
+    tdist.barrier()
+    torch.cuda.synchronize()
+    mlp.close()
+    tdist.barrier()
+    tdist.destroy_process_group()
 
 
 def main():

@@ -48,3 +48,33 @@ def test_sharding_on_two_gpus():
     res = _launch("gpu", 2, 600)
     assert res.returncode == 0 and "DIST-OK gpu" in res.stdout, res.stdout[-4000:]
     print("\n".join(l for l in res.stdout.splitlines() if "max rel err" in l))
+
+
+def test_push_staging_layout_matches_exchange_addressing():
+    """The GEMM epilogue of rank s stores row i of its partial sum into rank o's staging buffer float[world][m/world][n] at
+    slot s, row i - o*m/world (o = i // (m/world)); the exchange kernel on rank o reads partial[q] + i*n for its rows i.
+    With the offsets of push_slot_offset both must address the same element."""
+    import numpy as np
+    from awesome_fusion_b200 import dist as D
+    world, m, n = 4, 16, 8
+    rows = m // world
+    rng = np.random.default_rng(5)
+    partials = [rng.standard_normal((m, n)).astype(np.float32) for _ in range(world)]
+    stage = [np.zeros(world * rows * n, dtype=np.float32) for _ in range(world)]
+    for s_rank in range(world):          # what afb_gemm_launch_push does, element by element
+        for i in range(m):
+            o = i // rows
+            stage[o][(s_rank * rows + (i - o * rows)) * n:(s_rank * rows + (i - o * rows)) * n + n] = partials[s_rank][i]
+    for o in range(world):               # what afb_ksplit_allreduce_launch reads with the offsets of allreduce_pushed()
+        for i in range(o * rows, (o + 1) * rows):
+            acc = np.zeros(n, dtype=np.float32)
+            for q in range(world):
+                off = D.push_slot_offset(q, o, world, m, n)
+                assert off % 4 == 0
+                first = off // 4 + i * n
+                assert 0 <= first and first + n <= stage[o].size
+                acc += stage[o][first:first + n]
+            want = np.zeros(n, dtype=np.float32)
+            for q in range(world):
+                want += partials[q][i]
+            assert np.array_equal(acc, want)
