@@ -30,7 +30,13 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr int kRing = 4;                       // cp.async stages per warp (power of two)
+#ifndef AFB_DECODE_RING
+#define AFB_DECODE_RING 4
+#endif
+#ifndef AFB_DECODE_MT2_CTAS
+#define AFB_DECODE_MT2_CTAS 3
+#endif
+constexpr int kRing = AFB_DECODE_RING;         // cp.async stages per warp (power of two)
 constexpr int kStageBytes = 1024;              // 2 channels x 32 lanes x 16 bytes
 constexpr int kRingBytes = kWarps * kRing * kStageBytes;   // 32 KiB
 constexpr int kRedFloats = kWarps * 16 * 17;   // cross-warp reduction buffer, [warp][16 channels][<=16 rows + pad]; reuses the ring once the stream has ended
@@ -54,8 +60,12 @@ struct DecodeParams {
     uint32_t pass_k;  // k elements staged per pass (multiple of chunk * WK; m * (pass_k * 2 + 16) <= act_bytes)
     uint32_t group_shift;  // log2(group) (groups are powers of two)
     uint32_t slices;  // gridDim.y
-    float* ws;        // [slices][m][n] fp32 partial sums (slices > 1)
-    uint32_t* counters;  // one per CTA column, zero on entry, zero again on exit
+    // balanced form (streamk = 1): the grid is one wave of CTAs; the weights are cut into units of 16*wr channels x unit_k
+    // elements of K, numbered channel block major, and CTA c takes units [c*U/G, (c+1)*U/G): whole runs of K of one or more
+    // channel blocks.  A channel block shared by several CTAs is finished by the last of them to arrive, in CTA order.
+    uint32_t streamk, unit_k, units_per_cb, total_units;
+    float* ws;        // [contributor][m][n] fp32 partial sums (K-slices, or the CTAs sharing a channel block)
+    uint32_t* counters;  // one per channel block, zero on entry, zero again on exit
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -88,7 +98,9 @@ __device__ __forceinline__ float load_scale(const void* s, size_t idx, uint32_t 
 __device__ __forceinline__ uint32_t swz_piece(uint32_t pc) { return pc ^ (((pc >> 3) & 1u) << 1); }
 
 template <int BITS, int MT, bool GROUPED>
-__global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(const DecodeParams p) {
+// resident CTAs per SM the register budget is cut for: the group-scaled int4 kernel with 16 rows needs about 118 registers and
+// runs 12 % faster with two CTAs and no spills than with three CTAs squeezed into 80 (measured); the others gain nothing
+__global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : (BITS == 4 && GROUPED) ? 2 : AFB_DECODE_MT2_CTAS)) decode_kernel(const DecodeParams p) {
     constexpr int CH = BITS == 8 ? 64 : 128;    // k per chunk (a quad covers 64 bytes of one channel)
     constexpr int LK = CH / 4;                  // k per lane per chunk
     constexpr int AV = LK / 8;                  // 16-byte activation vectors per lane, row and chunk
@@ -101,16 +113,6 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const uint32_t wk_count = kWarps / p.wr;
     const uint32_t wr = warp / wk_count, wk = warp % wk_count;
-    const uint32_t nblk = blockIdx.x * 16 * p.wr;
-    const uint32_t row_a = nblk + wr * 16 + g, row_b = row_a + 8;
-    const bool ok_a = row_a < p.n, ok_b = row_b < p.n;
-    const uint8_t* pa = p.b + (size_t)(ok_a ? row_a : 0) * p.ldb_bytes + tig * 16;
-    const uint8_t* pb = p.b + (size_t)(ok_b ? row_b : 0) * p.ldb_bytes + tig * 16;
-    const uint32_t ks = blockIdx.y * p.kc;
-    const uint32_t kend = min(p.k, ks + p.kc);
-    const uint32_t nchunks = (kend - ks) / CH;
-    const uint32_t my_chunks = nchunks > wk ? (nchunks - wk + wk_count - 1) / wk_count : 0;
-    const size_t kbyte0 = BITS == 8 ? ks : (ks >> 1);
     const uint32_t xormask = (BITS == 8 && p.enc == AFB_ENC_OFFSET_BINARY) ? 0x80808080u : 0u;
     const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
     const uint32_t groups_per_row = GROUPED ? (p.k >> p.group_shift) : 0;
@@ -127,6 +129,31 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
     uint32_t act_off[AV];
 #pragma unroll
     for (int v = 0; v < AV; ++v) act_off[v] = (BITS == 4 ? swz_piece(tig * AV + v) : (uint32_t)(tig * AV + v)) * 16;
+
+    // ---- the pieces of work of this CTA: one (channel block, K range) in the grid form, a run of units in the balanced form
+    const uint32_t u_begin = p.streamk ? (uint32_t)((uint64_t)blockIdx.x * p.total_units / gridDim.x) : 0u;
+    const uint32_t u_end = p.streamk ? (uint32_t)((uint64_t)(blockIdx.x + 1) * p.total_units / gridDim.x) : 1u;
+    // CTA holding unit u of the balanced form: the largest c with c*U/G <= u
+    auto cta_of = [&](uint32_t u) { return (uint32_t)((((uint64_t)u + 1) * gridDim.x + p.total_units - 1) / p.total_units) - 1u; };
+    for (uint32_t u = u_begin; u < u_end;) {
+    uint32_t cb, ks, kend;
+    if (p.streamk) {
+        cb = u / p.units_per_cb;
+        const uint32_t ku0 = u - cb * p.units_per_cb, ku1 = min(p.units_per_cb, ku0 + (u_end - u));
+        ks = ku0 * p.unit_k; kend = ku1 * p.unit_k;
+        u += ku1 - ku0;
+    } else {
+        cb = blockIdx.x; ks = blockIdx.y * p.kc; kend = min(p.k, ks + p.kc);
+        u = u_end;
+    }
+    const uint32_t nblk = cb * 16 * p.wr;
+    const uint32_t row_a = nblk + wr * 16 + g, row_b = row_a + 8;
+    const bool ok_a = row_a < p.n, ok_b = row_b < p.n;
+    const uint8_t* pa = p.b + (size_t)(ok_a ? row_a : 0) * p.ldb_bytes + tig * 16;
+    const uint8_t* pb = p.b + (size_t)(ok_b ? row_b : 0) * p.ldb_bytes + tig * 16;
+    const uint32_t nchunks = (kend - ks) / CH;
+    const uint32_t my_chunks = nchunks > wk ? (nchunks - wk + wk_count - 1) / wk_count : 0;
+    const size_t kbyte0 = BITS == 8 ? ks : (ks >> 1);
 
     float acc[MT][4];
 #pragma unroll
@@ -258,7 +285,12 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
 
     const uint32_t rows_cta = 16 * p.wr;
     const uint32_t outputs = rows_cta * MCOLS;          // <= 2048
-    const bool single = p.slices == 1;
+    uint32_t contributors = p.slices, my_slot = blockIdx.y;
+    if (p.streamk) {   // the CTAs whose runs of units touch this channel block, in CTA order (= ascending K)
+        const uint32_t first = cta_of(cb * p.units_per_cb), last = cta_of(cb * p.units_per_cb + p.units_per_cb - 1);
+        contributors = last - first + 1; my_slot = blockIdx.x - first;
+    }
+    const bool single = contributors == 1;
     for (uint32_t idx = tid; idx < outputs; idx += kThreads) {
         const uint32_t mm = idx / rows_cta, r = idx - mm * rows_cta;   // consecutive threads -> consecutive channels
         const uint32_t nn = nblk + r;
@@ -270,38 +302,42 @@ __global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : 3)) decode_kernel(con
             if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
             p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
         } else {
-            __stcg(p.ws + ((size_t)blockIdx.y * p.m + mm) * p.n + nn, sum);
+            __stcg(p.ws + ((size_t)my_slot * p.m + mm) * p.n + nn, sum);
         }
     }
-    if (single) return;
-
-    // several K-slices: the last CTA of this column of CTAs adds the published partial sums in slice order
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const uint32_t old = atomicAdd(p.counters + blockIdx.x, 1u);
-        *s_last = (old == p.slices - 1) ? 1u : 0u;
-    }
-    __syncthreads();
-    if (!*s_last) return;
-    __threadfence();
-    for (uint32_t idx = tid; idx < p.m * rows_cta; idx += kThreads) {
-        const uint32_t mm = idx / rows_cta, nn = nblk + (idx % rows_cta);
-        if (nn >= p.n) continue;
-        const float* src = p.ws + (size_t)mm * p.n + nn;
-        const size_t slice_stride = (size_t)p.m * p.n;
-        float sum = 0.f;
-        for (uint32_t sl = 0; sl < p.slices; sl += 8) {  // eight independent loads in flight, summed in slice order
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = sl + i < p.slices ? __ldcg(src + (sl + i) * slice_stride) : 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sum += v[i];
+    if (!single) {
+        // several contributors (K-slices, or CTAs sharing the channel block): the last to arrive adds the published partial
+        // sums in contributor order (= ascending K), so the result does not depend on who that is
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t old = atomicAdd(p.counters + cb, 1u);
+            *s_last = (old == contributors - 1) ? 1u : 0u;
         }
-        if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
-        p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
+        __syncthreads();
+        if (*s_last) {
+            __threadfence();
+            for (uint32_t idx = tid; idx < p.m * rows_cta; idx += kThreads) {
+                const uint32_t mm = idx / rows_cta, nn = nblk + (idx % rows_cta);
+                if (nn >= p.n) continue;
+                const float* src = p.ws + (size_t)mm * p.n + nn;
+                const size_t slice_stride = (size_t)p.m * p.n;
+                float sum = 0.f;
+                for (uint32_t sl = 0; sl < contributors; sl += 8) {  // eight independent loads in flight, summed in order
+                    float v[8];
+#pragma unroll
+                    for (int i2 = 0; i2 < 8; ++i2) v[i2] = sl + i2 < contributors ? __ldcg(src + (sl + i2) * slice_stride) : 0.f;
+#pragma unroll
+                    for (int i2 = 0; i2 < 8; ++i2) sum += v[i2];
+                }
+                if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
+                p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
+            }
+            if (tid == 0) p.counters[cb] = 0u;  // ready for the next launch
+        }
     }
-    if (tid == 0) p.counters[blockIdx.x] = 0u;  // ready for the next launch
+    if (u < u_end) __syncthreads();   // the next piece reuses the ring (= the reduction buffer) and the flag word
+    }   // pieces of work
 }
 
 template <int BITS, int MT, bool GROUPED>
@@ -317,6 +353,30 @@ cudaError_t launch_one(const DecodeParams& p, dim3 grid, cudaStream_t s) {
     }
     kern<<<grid, kThreads, smem_bytes(MT), s>>>(p);
     return cudaGetLastError();
+}
+
+// CTAs of one kernel instance that fit an SM at the same time (asked once per instance and device).
+template <int BITS, int MT, bool GROUPED>
+int resident_one() {
+    static int cached_dev = -1, cached = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cached_dev != dev) {
+        auto kern = decode_kernel<BITS, MT, GROUPED>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT)) != cudaSuccess) return 0;
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem_bytes(MT)) != cudaSuccess) return 0;
+        cached = n; cached_dev = dev;
+    }
+    return cached;
+}
+int resident_ctas(uint32_t bits, int mt, bool grouped) {
+    if (bits == 8) {
+        if (mt == 1) return grouped ? resident_one<8, 1, true>() : resident_one<8, 1, false>();
+        return grouped ? resident_one<8, 2, true>() : resident_one<8, 2, false>();
+    }
+    if (mt == 1) return grouped ? resident_one<4, 1, true>() : resident_one<4, 1, false>();
+    return grouped ? resident_one<4, 2, true>() : resident_one<4, 2, false>();
 }
 
 }  // namespace
@@ -338,7 +398,7 @@ bool decode_supports(const afb_gemm_args& a) {
 //   * wr: activations are re-read by every column of CTAs, so more activation rows ask for more channels per CTA
 //     (keeps the activation traffic through L2 below about half of the weight traffic);
 //   * slices: only when the channel dimension alone cannot fill the GPU.
-static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, size_t counter_count, DecodeParams& p) {
+static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, DecodeParams& p) {
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
     const uint32_t sms = (uint32_t)sm_count;
     const uint32_t act_bytes_per_k = 2 * a.m;                      // per k, per column of CTAs
@@ -349,6 +409,11 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, si
     while (wr < 8 && ctas(wr * 2) >= 6 * sms) wr *= 2;              // plenty of channels: larger CTAs, fewer activation re-reads
     const size_t act_cap = (size_t)act_bytes(a.m <= 8 ? 1 : 2);
     while (wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > act_cap) wr *= 2;   // one round of the WK warps must fit the staging area
+    // the balanced form (below) pays off for more than 8 activation rows on large matrices (measured: 8 to 25 % there, a loss
+    // of up to 10 % for m <= 8, whose grid form needs no K-slices); it runs best with the widest CTA
+    bool want_balanced = weight_mb >= 48.0 && a.m > 8;
+    if (const char* e = getenv("AFB_DECODE_BALANCED")) want_balanced = atoi(e) != 0;   // tuning aid
+    if (want_balanced && (size_t)a.m * (ch * 2 + 16) <= act_cap) wr = 8;
     const uint32_t want = weight_mb < 48.0 ? sms * 3 / 2 : sms * 5;   // many small CTAs even out the load of the SMs (measured)
     uint32_t s = 1;
     const uint32_t unit = a.group_size > ch ? a.group_size : ch;
@@ -372,6 +437,35 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, size_t ws_bytes, si
     p.pass_k = ((p.kc + npass - 1) / npass + round - 1) / round * round;        // equal passes, whole rounds
     p.group_shift = 0;
     while (a.group_size && (1u << p.group_shift) < a.group_size) ++p.group_shift;
+
+    // Balanced form for large weight matrices: exactly one wave of CTAs, each streaming the same number of bytes.  The grid form
+    // above leaves SMs idle whenever channel blocks x slices is not a multiple of the resident CTAs (28672 channels: 448 CTAs on
+    // 444 places), and it cannot be fixed by another power-of-two split.
+    p.streamk = 0; p.unit_k = 0; p.units_per_cb = 0; p.total_units = 0;
+    const uint32_t unit_min = a.group_size > round ? a.group_size : round;   // whole rounds of the WK warps, whole scale groups
+    if (want_balanced && ctas_per_sm > 0 && a.k % unit_min == 0) {
+        const uint32_t cbs = ctas(wr);
+        uint32_t grid = sms * (uint32_t)ctas_per_sm;
+        uint32_t unit_k = unit_min;
+        while (a.k % (unit_k * 2) == 0 && (uint64_t)cbs * (a.k / (unit_k * 2)) >= 16ull * grid) unit_k *= 2;   // >= 16 units per CTA is balance enough
+        const uint32_t ku = a.k / unit_k;
+        const uint64_t total = (uint64_t)cbs * ku;
+        if (total < grid) grid = (uint32_t)total;
+        if (total < (1ull << 31)) {
+            auto cta_of = [&](uint64_t u) { return (uint32_t)(((u + 1) * grid + total - 1) / total) - 1u; };   // as in the kernel
+            uint32_t maxc = 1;
+            for (uint32_t cb = 0; cb < cbs; ++cb) {
+                const uint32_t c = cta_of((uint64_t)cb * ku + ku - 1) - cta_of((uint64_t)cb * ku) + 1;
+                if (c > maxc) maxc = c;
+            }
+            if ((size_t)maxc * a.m * a.n * sizeof(float) <= ws_bytes && cbs <= counter_count) {
+                p.streamk = 1; p.unit_k = unit_k; p.units_per_cb = ku; p.total_units = (uint32_t)total;
+                p.slices = grid;          // the launcher reads the grid size from here
+                p.kc = a.k;
+                p.pass_k = pass_max < a.k ? pass_max : (a.k + round - 1) / round * round;
+            }
+        }
+    }
 }
 
 int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t ws_bytes, uint32_t* counters,
@@ -385,11 +479,12 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
     p.m = a.m; p.n = a.n; p.k = a.k; p.lda = a.lda; p.ldc = a.ldc;
     p.ldb_bytes = a.b_bits == 8 ? a.ldb : a.ldb / 2;
     p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
-    pick_shape(a, ctx->sm_count, ws_bytes, counter_count, p);
-    p.ws = ws; p.counters = counters;
-    dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
     const bool grouped = a.group_size != 0;
     const int mt = a.m <= 8 ? 1 : 2;
+    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, p);
+    p.ws = ws; p.counters = counters;
+    dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
+    if (p.streamk) grid = dim3(p.slices, 1);
     cudaError_t e;
     if (a.b_bits == 8) {
         if (mt == 1) e = grouped ? launch_one<8, 1, true>(p, grid, s) : launch_one<8, 1, false>(p, grid, s);
