@@ -33,6 +33,9 @@ constexpr int kWarps = 8;
 #ifndef AFB_DECODE_RING
 #define AFB_DECODE_RING 4
 #endif
+#ifndef AFB_DECODE_MT1_CTAS
+#define AFB_DECODE_MT1_CTAS 4
+#endif
 #ifndef AFB_DECODE_MT2_CTAS
 #define AFB_DECODE_MT2_CTAS 3
 #endif
@@ -98,9 +101,10 @@ __device__ __forceinline__ float load_scale(const void* s, size_t idx, uint32_t 
 __device__ __forceinline__ uint32_t swz_piece(uint32_t pc) { return pc ^ (((pc >> 3) & 1u) << 1); }
 
 template <int BITS, int MT, bool GROUPED>
-// resident CTAs per SM the register budget is cut for: the group-scaled int4 kernel with 16 rows needs about 118 registers and
-// runs 12 % faster with two CTAs and no spills than with three CTAs squeezed into 80 (measured); the others gain nothing
-__global__ void __launch_bounds__(kThreads, (MT == 1 ? 4 : (BITS == 4 && GROUPED) ? 2 : AFB_DECODE_MT2_CTAS)) decode_kernel(const DecodeParams p) {
+// resident CTAs per SM the register budget is cut for: the group-scaled int4 kernels want more registers than the others (16 rows:
+// about 118, 12 % faster with two CTAs and no spills than with three squeezed into 80; 8 rows: 80, 3 to 8 % faster with three
+// CTAs than with four at 64); the other kernels gain nothing or lose (measured)
+__global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 3 : 2) : (MT == 1 ? AFB_DECODE_MT1_CTAS : AFB_DECODE_MT2_CTAS)) decode_kernel(const DecodeParams p) {
     constexpr int CH = BITS == 8 ? 64 : 128;    // k per chunk (a quad covers 64 bytes of one channel)
     constexpr int LK = CH / 4;                  // k per lane per chunk
     constexpr int AV = LK / 8;                  // 16-byte activation vectors per lane, row and chunk
