@@ -28,7 +28,7 @@ namespace {
 
 constexpr int BNW = 128;      // output channels per tile = TMEM lanes
 constexpr int BK = 64;
-constexpr int kSlotsA = 6;    // TMEM slots of converted weights
+constexpr int kSlotsA = 8;    // TMEM slots of converted weights (256 accumulator columns + 8 x 32 = all 512 columns)
 constexpr int kWorkerWarps = 8;   // measured: 8 beats 16 (1.10 vs 1.04 PFLOP/s on 2048 x 11008 x 4096)
 constexpr int kKParts = kWorkerWarps / 4;            // warps per TMEM lane quarter = parts the 64-wide K step is cut into
 constexpr int kKPer = BK / kKParts;                  // k per converter thread and stage (32 or 16)
