@@ -78,7 +78,7 @@ class ClockSampler:
             os.close(fd)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          "-lms", "25"], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
