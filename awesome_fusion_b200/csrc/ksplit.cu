@@ -330,6 +330,14 @@ extern "C" int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_d
     return launch_prefill_ts_tiles(*args, ctx, tile_done, (cudaStream_t)stream);
 }
 
+extern "C" int afb_abi_sizes(uint32_t sizes[3]) {
+    if (!sizes) return AFB_ERR_BAD_ARG;
+    sizes[0] = (uint32_t)sizeof(afb_gemm_args);
+    sizes[1] = (uint32_t)sizeof(afb_allreduce_args);
+    sizes[2] = (uint32_t)sizeof(afb_tile_allreduce_args);
+    return AFB_OK;
+}
+
 extern "C" int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream) {
     if (!args || !stage || !args->ptr_a || !args->ptr_b || !args->ptr_scale) return AFB_ERR_BAD_ARG;
     if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;

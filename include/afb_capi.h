@@ -191,6 +191,9 @@ int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* args, void* 
  * LOCAL slots (partial[q] = own_stage + (q * (M/world) - rank * (M/world)) * N floats, ld_partial = N): its first phase then
  * waits for every rank's GEMM, its sum reads local memory only, and its second phase broadcasts the bf16 rows. */
 int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream);
+/* sizeof(afb_gemm_args), sizeof(afb_allreduce_args), sizeof(afb_tile_allreduce_args) as this library was compiled: a binding
+ * in another language compares them with its own declarations before the first call.  Needs no GPU. */
+int afb_abi_sizes(uint32_t sizes[3]);
 /* fp32 [rows, cols] (ld_src) -> bf16 (ld_dst), round to nearest even: finishes a K-split whose partial
  * sums were combined by a library collective instead of afb_ksplit_allreduce_launch. */
 int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uint32_t cols, uint32_t ld_dst, uint32_t ld_src, void* stream);

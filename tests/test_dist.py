@@ -78,3 +78,14 @@ def test_push_staging_layout_matches_exchange_addressing():
             for q in range(world):
                 want += partials[q][i]
             assert np.array_equal(acc, want)
+
+
+def test_struct_layouts_match_the_library():
+    """The ctypes mirrors of the three argument blocks have the sizes the library was compiled with (no GPU needed)."""
+    import ctypes
+    import awesome_fusion_b200 as pkg
+    from awesome_fusion_b200 import dist as D
+    lib = pkg.load()
+    sizes = (ctypes.c_uint32 * 3)()
+    assert lib.lib.afb_abi_sizes(sizes) == 0
+    assert list(sizes) == [ctypes.sizeof(pkg.GemmArgs), ctypes.sizeof(D.AllReduceArgs), ctypes.sizeof(D.TileAllReduceArgs)]
