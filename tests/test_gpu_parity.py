@@ -272,3 +272,66 @@ def test_host_pointer_entry_point(afb, oracle, m, n, k):
     args = afb.make_args(c, case.a, case.b, case.scale, case.m, case.n, case.k, ldb=case.ldb)
     afb.gemm_host(args)
     check_close(oracle, oracle.gemm(case), c, "afb_gemm_host")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k,bits,group", [(16, 1000, 4096, 8, 0), (9, 2048, 8192, 4, 128), (16, 136, 1024, 8, 0), (12, 4104, 2048, 4, 0),
+                                               (16, 520, 2048, 8, 256), (3, 776, 4096, 4, 128)])
+def test_decode_balanced_form_on_ragged_shapes(afb, oracle, monkeypatch, m, n, k, bits, group):
+    """The one-wave form of the decode kernel (contiguous runs of K units per CTA, channel blocks shared between CTAs and
+    finished by the last to arrive) is chosen by itself only for large matrices; here it is forced on small and ragged
+    ones: channel counts that are no multiple of the CTA's block, fewer units than CTAs, every CTA shape."""
+    case = T.make_case(m, n, k, bits=bits, group=group, seed=81)
+    ref = oracle.gemm(case, threads=4)
+    monkeypatch.setenv("AFB_DECODE_BALANCED", "1")
+    outs = {}
+    for wr in ("1", "2", "4", "8"):
+        monkeypatch.setenv("AFB_DECODE_WR", wr)
+        a, _ = T.run_case(afb, case, variant=pkg.VARIANT_DECODE, guard=256)
+        b, raw = T.run_case(afb, case, variant=pkg.VARIANT_DECODE, guard=256)
+        assert np.array_equal(a, b), f"wr={wr}: two runs differ"
+        assert np.all(raw[:256] == 0xCD) and np.all(raw[-256:] == 0xCD)
+        check_close(oracle, ref, a, f"balanced decode wr={wr}")
+        outs[wr] = a
+    assert afb.read_status()[0] == 0
+    # the split-K workspace counters are back at zero: the grid form right after it must still be correct
+    monkeypatch.setenv("AFB_DECODE_BALANCED", "0")
+    monkeypatch.delenv("AFB_DECODE_WR")
+    c, _ = T.run_case(afb, case, variant=pkg.VARIANT_DECODE)
+    check_close(oracle, ref, c, "grid form after the balanced form")
+
+
+@pytest.mark.gpu
+def test_exchange_wait_runs_out_and_reports_status(afb, oracle):
+    """A bounded wait that nothing satisfies: the exchange kernel of a 2-rank job whose peer never signals gives up after
+    wait_ms, stores nothing, reports AFB_ERR_TIMEOUT with the place it gave up, and the device stays usable."""
+    import ctypes
+    from awesome_fusion_b200 import dist as D
+    m, n = 64, 256
+    partial, peer_partial = afb.malloc(m * n * 4), afb.malloc(m * n * 4)
+    c, peer_c = afb.malloc(m * n * 2), afb.malloc(m * n * 2)
+    sig, peer_sig = afb.malloc(2 * D.MAX_RANKS * 4), afb.malloc(2 * D.MAX_RANKS * 4)
+    try:
+        for p_, nb in ((partial, m * n * 4), (peer_partial, m * n * 4), (sig, 2 * D.MAX_RANKS * 4), (peer_sig, 2 * D.MAX_RANKS * 4)):
+            afb.memset(p_, 0, nb)
+        afb.memset(c, 0xCD, m * n * 2)
+        a = D.AllReduceArgs()
+        a.partial[0], a.partial[1] = partial, peer_partial
+        a.c[0], a.c[1] = c, peer_c
+        a.signals[0], a.signals[1] = sig, peer_sig       # "rank 1" is a buffer nobody writes: its signal never comes
+        a.rank, a.world, a.m, a.n, a.ld_partial, a.ldc, a.partial_f32 = 0, 2, m, n, n, n, 1
+        a.epoch, a.wait_ms, a.reserved, a.c_multicast = 1, 20, 0, None
+        f = afb.lib.afb_ksplit_allreduce_launch
+        f.argtypes = [ctypes.POINTER(D.AllReduceArgs), ctypes.c_void_p]
+        assert f(ctypes.byref(a), None) == 0
+        st = afb.read_status()                            # synchronises
+        assert st[0] == -4 and st[1] == 10 and st[2] == 0 and st[3] == 1, st      # AFB_ERR_TIMEOUT, phase-0 wait, rank 0, epoch 1
+        assert np.all(afb.to_host(c, (m * n * 2,), np.uint8) == 0xCD)             # nothing was stored
+        assert afb.read_status()[0] == 0                                          # reading cleared it
+        # the context is intact: an ordinary GEMM still runs and is right
+        case = T.make_case(4, 256, 512, seed=82)
+        out, _ = T.run_case(afb, case)
+        check_close(oracle, oracle.gemm(case, threads=2), out, "GEMM after a timed-out exchange")
+    finally:
+        for p_ in (partial, peer_partial, c, peer_c, sig, peer_sig):
+            afb.free(p_)
