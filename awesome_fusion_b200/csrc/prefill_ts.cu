@@ -48,6 +48,11 @@ struct TsParams {
     // optional (row-parallel reduce-scatter fused into the epilogue): fp32 C rows [o*push_rows, (o+1)*push_rows) go to rank o's
     // staging buffer, slot push_rank, instead of to p.c: push[o] + (push_rank * push_rows + local_row) * ldc + n
     float* push[AFB_MAX_RANKS];
+    // optional: the tiles beyond the last full wave (tail_first ..) are each cut into tail_parts stretches of K, one per CTA; the
+    // stretches meet as fp32 tiles in tail_ws ([tail tile][part][row][channel]) and the last CTA to arrive adds them in part order
+    uint32_t tail_first, tail_tiles, tail_parts;
+    float* tail_ws;
+    uint32_t* tail_counters;   // one per tail tile, zero on entry, zero again on exit
     uint32_t push_rows, push_rank;
     uint32_t push_on;      // 0: off; 1: the epilogue stores to the owner directly; 2: the epilogue stores to p.c (local) and the
                            // forwarder warps copy each finished tile to its owner while the next tile is being computed
@@ -63,7 +68,7 @@ struct TsLayout {
     static constexpr int kOffAct = 0;
     static constexpr int kOffRaw = kStages * kActBytes;
     static constexpr int kOffBars = kOffRaw + kStages * kRawBytes;
-    static constexpr int kNumBars = 3 * kStages + 2 * kSlotsA + 4;
+    static constexpr int kNumBars = 3 * kStages + 2 * kSlotsA + 6;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kDynamic = kOffMisc + 16 + 1024;
     static constexpr uint32_t kTmemCols = 512;                   // accumulator [0, BMA) + weight slots [256, 256 + kSlotsA * 32)
@@ -115,12 +120,29 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
     const uint32_t bar_acc_empty = bar_acc_full + 8u;
     const uint32_t bar_tile_stored = bar_acc_full + 16u;   // forward mode: the epilogue has stored a tile to local memory
     const uint32_t bar_tile_fwd = bar_acc_full + 24u;      // forward mode: the forwarder warps have copied it out
+    const uint32_t bar_tail_stored = bar_acc_full + 32u;   // tail stretch: every converter warp has published its part of the tile
+    const uint32_t bar_tail_verdict = bar_acc_full + 40u;  // tail stretch: the arrival count has been taken
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kOffMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t num_kb = p.k / BK;
     const uint32_t num_tiles = p.m_tiles * p.n_tiles;
+    // Work items of this CTA: its full tiles (t = blockIdx.x, + gridDim.x, ... below tail_first), then at most one stretch of K of
+    // a tail tile.  Every role walks the same list.
+    struct Item { uint32_t t, kb0, kb1, tail_r, part; bool tail; };
+    auto get_item = [&](uint32_t it, Item& w) -> bool {
+        const uint32_t t_full = blockIdx.x + it * gridDim.x;
+        if (t_full < p.tail_first) { w.t = t_full; w.kb0 = 0; w.kb1 = num_kb; w.tail = false; w.tail_r = 0; w.part = 0; return true; }
+        if (p.tail_parts && it == p.tail_first / gridDim.x && blockIdx.x < p.tail_tiles * p.tail_parts) {
+            w.tail_r = blockIdx.x / p.tail_parts; w.part = blockIdx.x - w.tail_r * p.tail_parts;
+            w.t = p.tail_first + w.tail_r;
+            w.kb0 = w.part * num_kb / p.tail_parts; w.kb1 = (w.part + 1) * num_kb / p.tail_parts;
+            w.tail = true;
+            return true;
+        }
+        return false;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty_act(s), 1); ptx::mbar_init(bar_empty_raw(s), kWorkerWarps); }
@@ -129,6 +151,8 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         ptx::mbar_init(bar_acc_empty, kWorkerWarps);
         ptx::mbar_init(bar_tile_stored, kWorkerWarps);
         ptx::mbar_init(bar_tile_fwd, kFwdWarps);
+        ptx::mbar_init(bar_tail_stored, kWorkerWarps);
+        ptx::mbar_init(bar_tail_verdict, 1);
         *abort_flag = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmap_act);
@@ -148,11 +172,13 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            Item w;
+            for (uint32_t it = 0; ok && get_item(it, w); ++it) {
+                const uint32_t t = w.t;
                 uint32_t mt_, nt_;
                 tile_coords(p, t, mt_, nt_);
                 const int m0 = (int)mt_ * BMA, n0 = (int)nt_ * BNW;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!wait_or_abort(bar_empty_act(stage), phase ^ 1u, abort_flag) ||
                         !wait_or_abort(bar_empty_raw(stage), phase ^ 1u, abort_flag)) {
                         if (!*abort_flag) { report_timeout(p.status, 21, (int)t, (int)kb); *abort_flag = 1; }
@@ -175,13 +201,15 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             constexpr uint32_t idesc = ptx::umma_idesc_bf16_f32(BNW, BMA);
             uint32_t st = 0, ph = 0, sa = 0, pa = 0, it = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            Item w;
+            for (; ok && get_item(it, w); ++it) {
+                const uint32_t t = w.t;
                 if (!wait_or_abort(bar_acc_empty, (it & 1u) ^ 1u, abort_flag)) {   // the epilogue of the previous tile has drained the accumulator
                     if (!*abort_flag) { report_timeout(p.status, 22, (int)t, -1); *abort_flag = 1; }
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_full_a(sa), pa, abort_flag)) {
                         if (!*abort_flag) { report_timeout(p.status, 23, (int)t, (int)kb); *abort_flag = 1; }
                         ok = false; break;
@@ -191,7 +219,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                     const uint32_t ta = tmem_base + L::kColA + sa * 32;
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j)   // 16 k per instruction: 8 TMEM columns of weights, 32 bytes of each activation row
-                        ptx::umma_bf16_ts(tmem_base, ta + 8 * j, db + 2u * j, idesc, (kb | (uint32_t)j) ? 1u : 0u);
+                        ptx::umma_bf16_ts(tmem_base, ta + 8 * j, db + 2u * j, idesc, ((kb - w.kb0) | (uint32_t)j) ? 1u : 0u);
                     ptx::umma_commit(bar_empty_act(st));
                     ptx::umma_commit(bar_empty_a(sa));
                     if (++st == S) { st = 0; ph ^= 1u; }
@@ -223,7 +251,9 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         }
         uint32_t st = 0, ph = 0, sa = 0, pa = 0, it = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        Item w;
+        for (; ok && get_item(it, w); ++it) {
+            const uint32_t t = w.t;
             uint32_t mt_, nt_;
             tile_coords(p, t, mt_, nt_);
             const uint32_t m0 = mt_ * BMA, n0 = nt_ * BNW;
@@ -233,8 +263,8 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 if (nn >= p.n || gidx >= groups_per_row) return (uint32_t)0;
                 return bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
             };
-            if (GROUPED) sc_nxt = load_gscale(0);
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+            if (GROUPED) sc_nxt = load_gscale(w.kb0 / kb_per_group);   // a stretch of K starts on a group boundary
+            for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
                 if (GROUPED && (kb % kb_per_group) == 0) { sc_cur = sc_nxt; sc_nxt = load_gscale(kb / kb_per_group + 1); }
                 if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_empty_a(sa), pa ^ 1u, abort_flag)) {
                     if (!*abort_flag) { report_timeout(p.status, 24, (int)t, (int)kb); *abort_flag = 1; }
@@ -300,7 +330,11 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 const uint32_t col = kq * kColsPerWarp + c0;
                 ptx::tmem_ld_32x32(tmem_base + ((q * 32u) << 16) + col, r);
                 ptx::tmem_ld_wait();
-                if (nn < p.n) {
+                if (w.tail) {   // a stretch of K of a tail tile: the raw fp32 sums go to the workspace, [part][row][channel]
+                    float* wsp = p.tail_ws + ((size_t)(w.tail_r * p.tail_parts + w.part) * BMA + col) * BNW + ch;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) __stcg(wsp + (size_t)j * BNW, __uint_as_float(r[j]));
+                } else if (nn < p.n) {
                     const uint32_t mrow = m0 + col;
                     if (p.c_f32) {
                         float* dst = reinterpret_cast<float*>(p.c) + (size_t)mrow * p.ldc + nn;
@@ -323,6 +357,72 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             if (p.tile_done) __threadfence_system();   // this lane's stores of the tile are visible to every GPU before the count below
             if (p.push_on == 2) __threadfence();       // ... and to the forwarder warps, which read them back through L2
             __syncwarp();
+            if (w.tail) {
+                // All stretches of the tile meet here.  The CTA that arrives last adds them in part order (so the bits do not
+                // depend on who that is), applies the channel scales, rounds and stores the tile.
+                // (a CTA has at most one such stretch per launch, so both barriers are used once: parity 0; every wait is bounded)
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_tail_stored);
+                if (warp == 2 && lane == 0) {
+                    if (wait_or_abort(bar_tail_stored, 0u, abort_flag)) {
+                        const uint32_t old = atomicAdd(p.tail_counters + w.tail_r, 1u);
+                        tmem_slot[2] = (old == p.tail_parts - 1) ? 1u : 0u;
+                    } else {
+                        tmem_slot[2] = 0u;
+                        if (!*abort_flag) { report_timeout(p.status, 28, (int)t, -1); *abort_flag = 1; }
+                    }
+                    ptx::mbar_arrive(bar_tail_verdict);
+                }
+                if (!wait_or_abort(bar_tail_verdict, 0u, abort_flag)) {
+                    if (!*abort_flag) { report_timeout(p.status, 29, (int)t, -1); *abort_flag = 1; }
+                    break;
+                }
+                if (tmem_slot[2]) {
+                    __threadfence();
+                    const uint32_t tid = threadIdx.x - 64;                  // 0 .. 255 over the converter warps
+                    const uint32_t c4 = tid & 31u, nv = n0 + c4 * 4;        // this thread's four channels (the same in every row)
+                    float sc4[4] = {1.f, 1.f, 1.f, 1.f};
+                    if (!GROUPED) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (nv + e < p.n)
+                                sc4[e] = p.scale_dtype == AFB_SCALE_BF16 ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(p.scale)[nv + e] << 16)
+                                                                         : reinterpret_cast<const float*>(p.scale)[nv + e];
+                    }
+                    const float* wst = p.tail_ws + (size_t)w.tail_r * p.tail_parts * BMA * BNW;
+                    constexpr uint32_t kVecs = BMA * (BNW / 4), kMaxParts = 4, kU = 4;
+                    for (uint32_t base = tid; base < kVecs; base += 256 * kU) {
+                        float4 v[kMaxParts][kU];
+#pragma unroll
+                        for (uint32_t j = 0; j < kMaxParts; ++j)
+#pragma unroll
+                            for (uint32_t u2 = 0; u2 < kU; ++u2)
+                                v[j][u2] = j < p.tail_parts ? __ldcg(reinterpret_cast<const float4*>(wst + (size_t)j * BMA * BNW) + base + u2 * 256)
+                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (uint32_t u2 = 0; u2 < kU; ++u2) {
+                            float4 a4 = v[0][u2];
+#pragma unroll
+                            for (uint32_t j = 1; j < kMaxParts; ++j)
+                                if (j < p.tail_parts) { a4.x += v[j][u2].x; a4.y += v[j][u2].y; a4.z += v[j][u2].z; a4.w += v[j][u2].w; }
+                            const uint32_t row = (base + u2 * 256) >> 5, mrow = m0 + row;
+                            if (mrow < p.m && nv < p.n) {
+                                a4.x *= sc4[0]; a4.y *= sc4[1]; a4.z *= sc4[2]; a4.w *= sc4[3];
+                                if (p.c_f32) {
+                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) + (size_t)mrow * p.ldc + nv) = a4;
+                                } else {
+                                    const __nv_bfloat162 lo = __floats2bfloat162_rn(a4.x, a4.y), hi = __floats2bfloat162_rn(a4.z, a4.w);
+                                    uint2 o2;
+                                    o2.x = *reinterpret_cast<const uint32_t*>(&lo); o2.y = *reinterpret_cast<const uint32_t*>(&hi);
+                                    *reinterpret_cast<uint2*>(p.c + (size_t)mrow * p.ldc + nv) = o2;
+                                }
+                            }
+                        }
+                    }
+                    if (tid == 0) p.tail_counters[w.tail_r] = 0u;   // ready for the next launch
+                }
+            }
             if (lane == 0) {
                 ptx::mbar_arrive(bar_acc_empty);
                 if (p.push_on == 2) ptx::mbar_arrive(bar_tile_stored);
@@ -436,6 +536,25 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
     p.group_m = tile_done ? p.m_tiles : pick_group_m(a, p.m_tiles, p.n_tiles, BMA, ctx->sm_count);   // the exchange kernel assumes row-tile-fastest order
     p.tile_done = tile_done;
+    // The tiles beyond the last full wave would keep a few SMs busy for a whole tile while the rest idle: cut each of them into
+    // up to 4 stretches of K, one per CTA (up-projection shard on 8 GPUs: 448 tiles on 148 SMs = 3 waves + 4 tiles).
+    p.tail_first = p.m_tiles * p.n_tiles; p.tail_tiles = 0; p.tail_parts = 0;
+    p.tail_ws = ctx->splitk_ws; p.tail_counters = ctx->splitk_counters;
+    {
+        const uint32_t tiles_all = p.m_tiles * p.n_tiles, sms = (uint32_t)ctx->sm_count, nkb = a.k / BK;
+        const uint32_t rest = tiles_all > sms ? tiles_all % sms : 0;
+        const char* e = getenv("AFB_PREFILL_SPLIT_TAIL");   // tuning aid: 0 switches it off
+        const bool allowed = !(e && atoi(e) == 0) && !tile_done && !push && a.n % 4 == 0;
+        if (allowed && rest > 0 && rest <= sms / 2) {
+            uint32_t parts = sms / rest;
+            if (parts > 4) parts = 4;
+            const uint32_t kb_group = GROUPED ? a.group_size / BK : 1;
+            while (parts >= 2 && (nkb % parts != 0 || (nkb / parts) % kb_group != 0 || nkb / parts < 8)) --parts;
+            if (parts >= 2 && (size_t)rest * parts * BMA * BNW * sizeof(float) <= ctx->splitk_ws_bytes && rest <= ctx->splitk_counter_count) {
+                p.tail_first = tiles_all - rest; p.tail_tiles = rest; p.tail_parts = parts;
+            }
+        }
+    }
     p.push_on = push ? (push_via_local ? 2u : 1u) : 0u;
     p.push_rank = push_rank;
     p.push_rows = push ? a.m / push_world : 0;

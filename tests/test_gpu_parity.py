@@ -335,3 +335,33 @@ def test_exchange_wait_runs_out_and_reports_status(afb, oracle):
     finally:
         for p_ in (partial, peer_partial, c, peer_c, sig, peer_sig):
             afb.free(p_)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,group,c_f32", [(8, 0, False), (4, 128, False), (8, 0, True)])
+def test_prefill_tail_tiles_split_along_k(afb, oracle, monkeypatch, bits, group, c_f32):
+    """150 tiles on 148 SMs: the two tiles beyond the last full wave are each cut into stretches of K that different CTAs
+    compute; the last CTA to arrive adds the stretches in order.  Checked against the oracle, for repeatability, and against
+    the same GEMM with the split switched off."""
+    if afb.sm_count() != 148:
+        pytest.skip("the shape is chosen for 148 SMs")
+    case = T.make_case(2560, 1920, 2048, bits=bits, group=group, seed=91)
+    ref = oracle.gemm(case, threads=8)
+    flags = pkg.FLAG_PREFILL_TMEM_A
+    a, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags, c_f32=c_f32)
+    b, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags, c_f32=c_f32)
+    assert np.array_equal(a, b), "two runs differ"
+    monkeypatch.setenv("AFB_PREFILL_SPLIT_TAIL", "0")
+    whole, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags, c_f32=c_f32)
+    assert afb.read_status()[0] == 0
+    if c_f32:
+        tol = 1e-5 * max(1.0, float(np.abs(ref).max()))
+        assert np.abs(a - ref).max() <= 2e-3 * T.rms(ref) + tol and np.abs(whole - ref).max() <= 2e-3 * T.rms(ref) + tol
+        assert not np.array_equal(a[:, -256:], np.zeros_like(a[:, -256:]))
+    else:
+        grouped = group != 0
+        check_close(oracle, ref, a, "tail split", tol=1.5e-2 if grouped else TOL, floor_frac=1.0 if grouped else FLOOR_FRAC)
+        check_close(oracle, ref, whole, "no tail split", tol=1.5e-2 if grouped else TOL, floor_frac=1.0 if grouped else FLOOR_FRAC)
+    # the split only changes the order of the fp32 additions of the two tail tiles: everything else is bit-identical
+    same = np.mean(a == whole)
+    assert same > 0.97, same
