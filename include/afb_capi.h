@@ -109,7 +109,10 @@ int afb_device_sync(void);
 /* ---- the hot path ------------------------------------------------------------- */
 /* hipModuleLaunchKernel (bfAintBGemm.cc:152,176): validates args, picks the variant,
  * decides grid/block/shared memory/tensor maps itself and launches asynchronously on
- * `stream` (NULL = the default stream).  Pointers are DEVICE pointers.               */
+ * `stream` (NULL = the default stream).  Pointers are DEVICE pointers.
+ * GEMMs that split K between CTAs (decode K-slices, short last wave of prefill tiles) use
+ * the context's fp32 workspace: two launches on one device must not overlap on the GPU
+ * (one stream per device serialises them).                                             */
 int afb_gemm_launch(const afb_gemm_args* args, void* stream);
 /* Which variant AFB_VARIANT_AUTO resolves to for these args (no launch). */
 int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
