@@ -42,6 +42,7 @@ struct TsParams {
     uint32_t m, n, k, ldc;
     uint32_t enc, scale_dtype, group;
     uint32_t m_tiles, n_tiles;
+    uint32_t m_rot;        // row tiles are taken in rotated order, starting at this one (spreads the peers a rank pushes to)
     uint32_t group_m;      // tile order: groups of group_m row tiles; inside a group the channel tiles advance, row tile fastest
     uint32_t c_f32;
     uint32_t* tile_done;   // optional: per-tile counters, +kWorkerWarps when a tile of C has been stored (system-scope release)
@@ -82,7 +83,8 @@ __device__ __forceinline__ void tile_coords(const TsParams& p, uint32_t t, uint3
     const uint32_t g = t / per_group, r = t - g * per_group;
     const uint32_t gsz = min(p.group_m, p.m_tiles - g * p.group_m);
     n_tile = r / gsz;
-    m_tile = g * p.group_m + (r - n_tile * gsz);
+    m_tile = g * p.group_m + (r - n_tile * gsz) + p.m_rot;
+    if (m_tile >= p.m_tiles) m_tile -= p.m_tiles;
 }
 
 __device__ __forceinline__ void report_timeout(int32_t* status, int where, int a, int b) {
@@ -556,6 +558,13 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
         }
     }
     p.push_on = push ? (push_via_local ? 2u : 1u) : 0u;
+    // every rank walks the row tiles from a different start, so that at any moment the ranks push to different owners
+    // instead of all loading the same peer's NVLink ingress
+    p.m_rot = 0;
+    if (push) {
+        const char* e = getenv("AFB_PUSH_ROTATE");   // tuning aid: 0 switches the rotation off
+        if (!(e && atoi(e) == 0)) p.m_rot = (uint32_t)(((uint64_t)push_rank * p.m_tiles) / push_world) % p.m_tiles;
+    }
     p.push_rank = push_rank;
     p.push_rows = push ? a.m / push_world : 0;
     for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push[q] = (push && q < push_world) ? reinterpret_cast<float*>(push[q]) : nullptr;
