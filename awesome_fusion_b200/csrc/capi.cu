@@ -209,7 +209,19 @@ int afb_gemm_launch(const afb_gemm_args* args, void* stream) {
         case AFB_VARIANT_PREFILL: {
             // two implementations of the prefill variant; a flag or AFB_PREFILL_IMPL=ss|ts overrides the default
             static const int env_ts = [] { const char* e = getenv("AFB_PREFILL_IMPL"); return e ? (e[0] == 't' ? 1 : 0) : -1; }();
-            bool ts = env_ts < 0 ? args->m > kPrefillTsMinM : env_ts == 1;
+            bool ts = env_ts == 1;
+            if (env_ts < 0) {
+                ts = args->m > kPrefillTsMinM;
+                if (!ts) {
+                    // up to 128 rows both forms are bound by the weight conversion: the shared-memory form converts 256 channels
+                    // per tile, the tensor-memory form 128 (about 0.7 of the time, measured); what decides is how many waves of
+                    // tiles each needs (28672 channels: 112 vs 224 tiles on 148 SMs -> shared-memory form; 8192: 32 vs 64 -> the other)
+                    const uint64_t sms = (uint64_t)ctx->sm_count, mt = (args->m + 127) / 128;
+                    const uint64_t waves_ss = (mt * ((args->n + 255) / 256) + sms - 1) / sms;
+                    const uint64_t waves_ts = (mt * ((args->n + 127) / 128) + sms - 1) / sms;
+                    ts = waves_ts * 7 < waves_ss * 10;
+                }
+            }
             if (args->flags & AFB_FLAG_PREFILL_SMEM_B) ts = false;
             if (args->flags & AFB_FLAG_PREFILL_TMEM_A) ts = true;
             return ts ? launch_prefill_ts(*args, ctx, s) : launch_prefill(*args, ctx, s);
