@@ -62,3 +62,28 @@ def test_validation_without_gpu(lib):
 def test_missing_library_fails_loudly(tmp_path):
     with pytest.raises(pkg.AfbError):
         pkg.Library(str(tmp_path / "nope.so"))
+
+
+def test_balanced_decode_partition_arithmetic():
+    """The one-wave form of the decode kernel gives CTA c the units [c*U/G, (c+1)*U/G) and finds the CTA of unit u as
+    ceil((u+1)*G/U) - 1 (csrc/decode.cu, kernel and pick_shape use the same two formulas).  Restated here and checked:
+    the runs tile [0, U) exactly, the inverse agrees with them, and the contributors of a channel block are consecutive CTAs."""
+    def start(c, U, G):
+        return c * U // G
+
+    def cta_of(u, U, G):
+        return ((u + 1) * G + U - 1) // U - 1
+
+    for cbs, ku, G in [(224, 32, 444), (896, 16, 592), (2, 16, 32), (1792, 16, 592), (63, 8, 444), (7, 64, 296), (448, 5, 444)]:
+        U = cbs * ku
+        G = min(G, U)
+        owner = [None] * U
+        for c in range(G):
+            for u in range(start(c, U, G), start(c + 1, U, G)):
+                assert owner[u] is None
+                owner[u] = c
+        assert all(o is not None for o in owner)                       # every unit has exactly one CTA
+        assert all(cta_of(u, U, G) == owner[u] for u in range(U))      # the closed form finds it
+        for cb in range(cbs):
+            first, last = cta_of(cb * ku, U, G), cta_of(cb * ku + ku - 1, U, G)
+            assert sorted(set(owner[cb * ku:(cb + 1) * ku])) == list(range(first, last + 1))
