@@ -5,18 +5,12 @@ plus the C++ host driver in ``driver/``.  This Python package is the thin host-s
 the tests, the benchmark and the multi-GPU launcher use; it never computes anything itself
 and raises if the CUDA library is missing.
 """
-from .capi import (  # noqa: F401
-    AfbError,
-    GemmArgs,
-    Library,
-    ENC_TWOS, ENC_OFFSET, LAYOUT_ROW, LAYOUT_COL, SCALE_F32, SCALE_BF16,
-    VARIANT_AUTO, VARIANT_DECODE, VARIANT_PREFILL, VARIANT_NAIVE, FLAG_C_F32, FLAG_PREFILL_SMEM_B, FLAG_PREFILL_TMEM_A, FLAG_PUSH_VIA_LOCAL,
-    library_path, load,
-)
+from . import capi as _capi
+from .capi import AfbError, GemmArgs, Library, library_path, load  # noqa: F401
 from .build import build_library  # noqa: F401
 
-__all__ = [
-    "AfbError", "GemmArgs", "Library", "library_path", "load", "build_library",
-    "ENC_TWOS", "ENC_OFFSET", "LAYOUT_ROW", "LAYOUT_COL", "SCALE_F32", "SCALE_BF16",
-    "VARIANT_AUTO", "VARIANT_DECODE", "VARIANT_PREFILL", "VARIANT_NAIVE", "FLAG_C_F32", "FLAG_PREFILL_SMEM_B", "FLAG_PREFILL_TMEM_A", "FLAG_PUSH_VIA_LOCAL",
-]
+# every ENC_ / LAYOUT_ / SCALE_ / VARIANT_ / FLAG_ / ACT_ constant of include/afb_capi.h
+_CONSTANTS = [n for n in dir(_capi) if n.split("_")[0] in ("ENC", "LAYOUT", "SCALE", "VARIANT", "FLAG", "ACT", "PACK")]
+globals().update({n: getattr(_capi, n) for n in _CONSTANTS})
+
+__all__ = ["AfbError", "GemmArgs", "Library", "library_path", "load", "build_library"] + _CONSTANTS

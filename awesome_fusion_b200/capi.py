@@ -17,6 +17,8 @@ FLAG_C_F32 = 1
 FLAG_PREFILL_SMEM_B = 2
 FLAG_PREFILL_TMEM_A = 4
 FLAG_PUSH_VIA_LOCAL = 8
+FLAG_DUMP_DECODE_PAIRING = 16
+FLAG_GROUP_EXACT = 32
 IPC_HANDLE_BYTES = 64
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

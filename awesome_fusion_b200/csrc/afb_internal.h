@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda.h>
 #include <stdint.h>
+#include <atomic>
 #include "afb_capi.h"
 
 namespace afb {
@@ -13,11 +14,20 @@ struct DeviceCtx {
     int      device = -1;
     int      sm_count = 0;
     int32_t* status = nullptr;        // device int32[4]: {code, where, a, b}
-    // split-K workspace of the decode kernel: fp32 partial sums + per-row-block arrival counters
-    float*    splitk_ws = nullptr;
-    size_t    splitk_ws_bytes = 0;
-    uint32_t* splitk_counters = nullptr;
-    size_t    splitk_counter_count = 0;
+    // Split-K workspaces (fp32 partial sums + arrival counters, used by decode K-slices, the balanced decode form and the
+    // prefill tail split): one per stream that has launched such a GEMM, so that launches on different streams never share
+    // one.  Slot 0 is allocated by afb_init, the others on a stream's first launch (outside any stream capture).
+    static constexpr int kMaxWorkspaces = 16;
+    struct Workspace {
+        bool          assigned = false;
+        cudaStream_t  stream = nullptr;
+        float*        ws = nullptr;
+        uint32_t*     counters = nullptr;
+    };
+    Workspace workspaces[kMaxWorkspaces];
+    size_t    splitk_ws_bytes = 0;        // size of every workspace
+    size_t    splitk_counter_count = 0;   // counters of every workspace
+    uint32_t* ar_words = nullptr;         // device uint32[4]: hand-off words of the two exchange kernels (CTAs finished, any failed)
     // staging for afb_gemm_host (grow-only)
     void*  stage[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t stage_bytes[4] = {0, 0, 0, 0};
@@ -26,7 +36,17 @@ struct DeviceCtx {
     cudaEvent_t host_ev[2 * 16 + 2] = {};
 };
 
+// "Done once per device" for function-local statics (kernel attributes, occupancy queries).  One bit per device; what it
+// guards is idempotent, so two host threads that both find the bit clear simply both do the work.
+struct DeviceOnce {
+    std::atomic<uint32_t> mask{0};
+    bool done(int dev) const { return (mask.load(std::memory_order_acquire) >> (dev & 31)) & 1u; }
+    void mark(int dev) { mask.fetch_or(1u << (dev & 31), std::memory_order_release); }
+};
+
 DeviceCtx* current_ctx();           // nullptr when afb_init was not called on the current device
+// The split-K workspace of `s` on this device (allocates it on the stream's first use); nullptr + *rc on failure.
+const DeviceCtx::Workspace* workspace_for(DeviceCtx* ctx, cudaStream_t s, int* rc);
 int  cuda_fail(cudaError_t e);      // records e, returns AFB_ERR_CUDA
 void count_launch(unsigned n = 1);
 

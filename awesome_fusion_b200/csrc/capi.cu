@@ -33,6 +33,31 @@ DeviceCtx* current_ctx() {
     return g_ctx[dev].ready ? &g_ctx[dev] : nullptr;
 }
 
+const DeviceCtx::Workspace* workspace_for(DeviceCtx* ctx, cudaStream_t s, int* rc) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceCtx::Workspace* free_slot = nullptr;
+    for (auto& w : ctx->workspaces) {
+        if (w.assigned && w.stream == s) return &w;
+        if (!w.assigned && !free_slot) free_slot = &w;
+    }
+    if (!free_slot) { *rc = AFB_ERR_TOO_LARGE; return nullptr; }   // more streams than workspaces
+    if (!free_slot->ws) {
+        cudaError_t e = cudaMalloc(&free_slot->ws, ctx->splitk_ws_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&free_slot->counters, ctx->splitk_counter_count * sizeof(uint32_t));
+        if (e == cudaSuccess) e = cudaMemset(free_slot->counters, 0, ctx->splitk_counter_count * sizeof(uint32_t));
+        if (e != cudaSuccess) {
+            if (free_slot->ws) cudaFree(free_slot->ws);
+            if (free_slot->counters) cudaFree(free_slot->counters);
+            free_slot->ws = nullptr; free_slot->counters = nullptr;
+            *rc = cuda_fail(e);
+            return nullptr;
+        }
+    }
+    free_slot->assigned = true;
+    free_slot->stream = s;
+    return free_slot;
+}
+
 EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
@@ -53,11 +78,15 @@ static int validate(const afb_gemm_args* a) {
     if (a->reserved != 0) return AFB_ERR_BAD_ARG;
     if (a->b_bits != 8 && a->b_bits != 4) return AFB_ERR_BAD_ARG;
     if (a->b_encoding > 1 || a->b_layout > 1 || a->scale_dtype > 1 || a->variant > 3) return AFB_ERR_BAD_ARG;
-    if (a->flags & ~(AFB_FLAG_C_F32 | AFB_FLAG_PREFILL_SMEM_B | AFB_FLAG_PREFILL_TMEM_A)) return AFB_ERR_BAD_ARG;
+    if (a->flags & ~(AFB_FLAG_C_F32 | AFB_FLAG_PREFILL_SMEM_B | AFB_FLAG_PREFILL_TMEM_A | AFB_FLAG_GROUP_EXACT)) return AFB_ERR_BAD_ARG;
+    if ((a->flags & AFB_FLAG_GROUP_EXACT) && (a->flags & AFB_FLAG_PREFILL_SMEM_B) && a->group_size) return AFB_ERR_UNSUPPORTED;   // only the tensor-memory form has it
     if (a->lda < a->k || a->ldc < a->n) return AFB_ERR_BAD_ARG;
     if (a->b_layout == AFB_LAYOUT_COL ? a->ldb < a->k : a->ldb < a->n) return AFB_ERR_BAD_ARG;
     if (a->b_bits == 4 && (a->b_layout != AFB_LAYOUT_COL || (a->k & 1) || (a->ldb & 1))) return AFB_ERR_UNSUPPORTED;
     if (a->group_size && (a->k % a->group_size)) return AFB_ERR_BAD_ARG;
+    // element alignment of what the kernels load and store as 2- or 4-byte words (a misaligned pointer would fault on the GPU)
+    if ((uintptr_t)a->ptr_scale % (a->scale_dtype == AFB_SCALE_BF16 ? 2 : 4)) return AFB_ERR_BAD_ARG;
+    if ((uintptr_t)a->ptr_c % ((a->flags & AFB_FLAG_C_F32) ? 4 : 2) || (uintptr_t)a->ptr_a % 2) return AFB_ERR_BAD_ARG;
     return AFB_OK;
 }
 
@@ -105,11 +134,13 @@ int afb_init(int device) {
     c.sm_count = prop.multiProcessorCount;
     AFB_CUDA(cudaMalloc(&c.status, 4 * sizeof(int32_t)));
     AFB_CUDA(cudaMemset(c.status, 0, 4 * sizeof(int32_t)));
-    AFB_CUDA(cudaMalloc(&c.splitk_ws, kSplitKWorkspaceBytes));
     c.splitk_ws_bytes = kSplitKWorkspaceBytes;
-    AFB_CUDA(cudaMalloc(&c.splitk_counters, kSplitKCounters * sizeof(uint32_t)));
-    AFB_CUDA(cudaMemset(c.splitk_counters, 0, kSplitKCounters * sizeof(uint32_t)));
     c.splitk_counter_count = kSplitKCounters;
+    AFB_CUDA(cudaMalloc(&c.workspaces[0].ws, kSplitKWorkspaceBytes));
+    AFB_CUDA(cudaMalloc(&c.workspaces[0].counters, kSplitKCounters * sizeof(uint32_t)));
+    AFB_CUDA(cudaMemset(c.workspaces[0].counters, 0, kSplitKCounters * sizeof(uint32_t)));
+    AFB_CUDA(cudaMalloc(&c.ar_words, 4 * sizeof(uint32_t)));
+    AFB_CUDA(cudaMemset(c.ar_words, 0, 4 * sizeof(uint32_t)));
     AFB_CUDA(cudaDeviceSynchronize());
     c.ready = true;
     return AFB_OK;
@@ -122,7 +153,8 @@ int afb_finalize(void) {
     DeviceCtx& c = g_ctx[dev];
     if (!c.ready) return AFB_OK;
     cudaDeviceSynchronize();
-    cudaFree(c.status); cudaFree(c.splitk_ws); cudaFree(c.splitk_counters);
+    cudaFree(c.status); cudaFree(c.ar_words);
+    for (auto& w : c.workspaces) { if (w.ws) cudaFree(w.ws); if (w.counters) cudaFree(w.counters); }
     for (int i = 0; i < 4; ++i) if (c.stage[i]) cudaFree(c.stage[i]);
     if (c.host_in) {
         cudaStreamDestroy(c.host_in); cudaStreamDestroy(c.host_out);
@@ -224,6 +256,7 @@ int afb_gemm_launch(const afb_gemm_args* args, void* stream) {
             }
             if (args->flags & AFB_FLAG_PREFILL_SMEM_B) ts = false;
             if (args->flags & AFB_FLAG_PREFILL_TMEM_A) ts = true;
+            if ((args->flags & AFB_FLAG_GROUP_EXACT) && args->group_size) ts = true;
             return ts ? launch_prefill_ts(*args, ctx, s) : launch_prefill(*args, ctx, s);
         }
         default:                  return launch_naive(*args, ctx, s);
@@ -329,6 +362,14 @@ int afb_read_status(int32_t out[4]) {
     AFB_CUDA(cudaDeviceSynchronize());
     AFB_CUDA(cudaMemcpy(out, ctx->status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost));
     AFB_CUDA(cudaMemset(ctx->status, 0, 4 * sizeof(int32_t)));
+    if (out[0] != 0) {
+        // A wait that gave up may have left arrival counters half way (a CTA that aborted never counted itself): launches that
+        // were in flight with it are void, and the counters go back to zero so that the next launch starts clean.
+        std::lock_guard<std::mutex> lock(g_mutex);
+        for (auto& w : ctx->workspaces)
+            if (w.counters) AFB_CUDA(cudaMemset(w.counters, 0, ctx->splitk_counter_count * sizeof(uint32_t)));
+        AFB_CUDA(cudaMemset(ctx->ar_words, 0, 4 * sizeof(uint32_t)));
+    }
     return AFB_OK;
 }
 

@@ -347,13 +347,13 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
 template <int BITS, int MT, bool GROUPED>
 cudaError_t launch_one(const DecodeParams& p, dim3 grid, cudaStream_t s) {
     auto kern = decode_kernel<BITS, MT, GROUPED>;
-    static int attr_dev = -1;   // per template instance
+    static DeviceOnce attr_set;   // per template instance
     int dev = 0;
     cudaGetDevice(&dev);
-    if (attr_dev != dev) {
+    if (!attr_set.done(dev)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT));
         if (e != cudaSuccess) return e;
-        attr_dev = dev;
+        attr_set.mark(dev);
     }
     kern<<<grid, kThreads, smem_bytes(MT), s>>>(p);
     return cudaGetLastError();
@@ -362,17 +362,17 @@ cudaError_t launch_one(const DecodeParams& p, dim3 grid, cudaStream_t s) {
 // CTAs of one kernel instance that fit an SM at the same time (asked once per instance and device).
 template <int BITS, int MT, bool GROUPED>
 int resident_one() {
-    static int cached_dev = -1, cached = 0;
+    static std::atomic<int> cached[32];   // 0 = not asked yet (zero-initialised)
     int dev = 0;
     cudaGetDevice(&dev);
-    if (cached_dev != dev) {
+    int n = cached[dev & 31].load(std::memory_order_acquire);
+    if (n == 0) {
         auto kern = decode_kernel<BITS, MT, GROUPED>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT)) != cudaSuccess) return 0;
-        int n = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem_bytes(MT)) != cudaSuccess) return 0;
-        cached = n; cached_dev = dev;
+        cached[dev & 31].store(n, std::memory_order_release);
     }
-    return cached;
+    return n;
 }
 int resident_ctas(uint32_t bits, int mt, bool grouped) {
     if (bits == 8) {
@@ -505,7 +505,10 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
 }
 
 int launch_decode(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
-    return launch_decode_ws(a, ctx, ctx->splitk_ws, ctx->splitk_ws_bytes, ctx->splitk_counters, ctx->splitk_counter_count, s);
+    int rc = AFB_OK;
+    const DeviceCtx::Workspace* w = workspace_for(ctx, s, &rc);
+    if (!w) return rc;
+    return launch_decode_ws(a, ctx, w->ws, ctx->splitk_ws_bytes, w->counters, ctx->splitk_counter_count, s);
 }
 
 }  // namespace afb

@@ -47,6 +47,12 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
     return d;
 }
 
+__device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // x holds two two's-complement int8 values in bits [0,8) and [16,24) (other bits ignored).
 // Returns the two exact bf16 values, low half = the value from bits [0,8).
 __device__ __forceinline__ uint32_t s8pair_to_bf16x2(uint32_t x) {

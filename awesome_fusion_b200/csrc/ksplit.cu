@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
         }
         const bool ok = wait_all(my_sig, 0, p.world, p.epoch, p.wait_ns);
         if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 10; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
+        if (!ok) atomicExch(p.cta_done + 1, 1u);   // every CTA runs its own clock: one that gave up vetoes the completion signal
         s_ok = ok ? 1u : 0u;
     }
     __syncthreads();
@@ -135,9 +136,10 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
     }
     __syncthreads();
     if (s_last && threadIdx.x == 0) {
+        const bool any_failed = atomicExch(p.cta_done + 1, 0u) != 0;
         *p.cta_done = 0u;
         __threadfence_system();
-        if (s_ok) {   // after a timeout nothing was stored: do not claim completion
+        if (!any_failed) {   // after a timeout in ANY CTA part of the block was not stored: do not claim completion
             for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 1 * AFB_MAX_RANKS + p.rank, p.epoch);
             const bool ok = wait_all(my_sig, 1, p.world, p.epoch, p.wait_ns);
             if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 11; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
@@ -255,10 +257,8 @@ __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(uint16_t* __restrict
     }
 }
 
-uint32_t* g_cta_done[32] = {nullptr};      // two words per device: CTAs finished, any-CTA-failed
-uint32_t* g_cta_done_tile[32] = {nullptr}; // the tile-granular kernel may overlap the plain one: its own pair
-
 }  // namespace
+
 }  // namespace afb
 
 using namespace afb;
@@ -275,12 +275,6 @@ extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* st
     if ((uintptr_t)a->c_multicast % 16) return AFB_ERR_BAD_ARG;
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;
-    if (!g_cta_done[ctx->device]) {
-        cudaError_t e = cudaMalloc(&g_cta_done[ctx->device], 2 * sizeof(uint32_t));
-        if (e != cudaSuccess) return cuda_fail(e);
-        e = cudaMemset(g_cta_done[ctx->device], 0, 2 * sizeof(uint32_t));
-        if (e != cudaSuccess) return cuda_fail(e);
-    }
     ARParams p;
     for (int q = 0; q < AFB_MAX_RANKS; ++q) {
         p.partial[q] = q < (int)a->world ? a->partial[q] : nullptr;
@@ -291,7 +285,7 @@ extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* st
     p.partial_f32 = a->partial_f32; p.epoch = a->epoch;
     p.c_multicast = reinterpret_cast<uint16_t*>(a->c_multicast);
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
-    p.cta_done = g_cta_done[ctx->device];
+    p.cta_done = ctx->ar_words;          // words 0-1: this kernel
     p.status = ctx->status;
     const int grid = ctx->sm_count;   // one CTA per SM: all CTAs are co-resident, so the last-CTA hand-off cannot starve
     if (a->partial_f32) ksplit_allreduce_kernel<true><<<grid, kThreads, 0, (cudaStream_t)stream>>>(p);
@@ -371,12 +365,6 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
     }
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;
-    if (!g_cta_done_tile[ctx->device]) {
-        cudaError_t e = cudaMalloc(&g_cta_done_tile[ctx->device], 2 * sizeof(uint32_t));
-        if (e != cudaSuccess) return cuda_fail(e);
-        e = cudaMemset(g_cta_done_tile[ctx->device], 0, 2 * sizeof(uint32_t));
-        if (e != cudaSuccess) return cuda_fail(e);
-    }
     TileARParams tp;
     ARParams& p = tp.ar;
     for (int q = 0; q < AFB_MAX_RANKS; ++q) {
@@ -390,17 +378,17 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
     p.partial_f32 = 1; p.epoch = a->epoch;
     p.c_multicast = nullptr;   // the tile-granular form stores to each peer
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
-    p.cta_done = g_cta_done_tile[ctx->device];
+    p.cta_done = ctx->ar_words + 2;      // words 2-3: the tile-granular kernel may overlap the plain one
     p.status = ctx->status;
     tp.tile_m = tm; tp.tile_n = tn; tp.m_tiles = mt; tp.n_tiles = nt; tp.arrivals = arr; tp.tile_epoch = ta->tile_epoch;
     // One CTA per SM next to the GEMM's CTA (256 threads, no dynamic shared memory, <= 128 registers per thread).
     // The GEMM needs the SM's largest shared-memory carve-out; an SM cannot change its carve-out while a CTA is resident,
     // so this kernel asks for the same carve-out: whichever of the two reaches an SM first, the other can join it.
-    static int carveout_dev = -1;
-    if (carveout_dev != ctx->device) {
+    static DeviceOnce carveout_set;
+    if (!carveout_set.done(ctx->device)) {
         cudaError_t e = cudaFuncSetAttribute(ksplit_tile_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return cuda_fail(e);
-        carveout_dev = ctx->device;
+        carveout_set.mark(ctx->device);
     }
     // Few threads on purpose: the pulls are long-latency NVLink loads; a full-size CTA keeps so many of them in flight that the
     // SM's load/store path backs up and the GEMM's own shared-memory reads queue behind them (measured: the GEMM ran 2.3x slower).

@@ -94,6 +94,26 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
                 sc = bf16_dup(sb);
             }
             uint32_t* o = reinterpret_cast<uint32_t*>(out + (size_t)n * a.k + k0);
+            if (a.flags & AFB_FLAG_DUMP_DECODE_PAIRING) {
+                // the decode kernel's unpack: cheap pairing ({k0,k2},{k1,k3} / {k0,k4}..{k3,k7}), integers only (that kernel
+                // applies group scales to fp32 partial sums, never to weights); stored back in natural k order
+                uint16_t* o16 = out + (size_t)n * a.k + k0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (a.b_bits == 8) {
+                        uint32_t p02, p13;
+                        s8x4_to_bf16_strided(w[j] ^ xormask, p02, p13);
+                        o16[4 * j + 0] = (uint16_t)(p02 & 0xffff); o16[4 * j + 2] = (uint16_t)(p02 >> 16);
+                        o16[4 * j + 1] = (uint16_t)(p13 & 0xffff); o16[4 * j + 3] = (uint16_t)(p13 >> 16);
+                    } else {
+                        uint32_t p[4];
+                        s4x8_to_bf16_strided(w[j], magic4, p);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { o16[8 * j + i] = (uint16_t)(p[i] & 0xffff); o16[8 * j + 4 + i] = (uint16_t)(p[i] >> 16); }
+                    }
+                }
+                continue;
+            }
             if (a.b_bits == 8) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {

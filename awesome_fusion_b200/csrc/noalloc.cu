@@ -6,8 +6,13 @@
 // every stream that is running.  Such callers cannot use afb_init + afb_gemm_launch, because afb_init
 // allocates the split-K workspace.  This entry point needs no afb_init and never calls cudaMalloc,
 // cudaFree or any allocating routine: the split-K scratch (fp32 partial sums and the per-row-block
-// arrival counters) lives in a fixed array inside the library image.  Every GPU that loads libafb.so
-// holds that array (kScratchBytes + kCounters * 4 bytes) until the process exits, used or not.
+// arrival counters) lives in a fixed array inside the library image.  Every GPU on which the image
+// has been placed holds that array (kScratchBytes + kCounters * 4 bytes) until the process exits.
+// With CUDA's default lazy module loading the driver places the image -- this array and the decode
+// kernels -- when they are first touched, i.e. inside the FIRST call of this entry point on a device
+// (cudaGetSymbolAddress, then the first launch).  That one call can therefore still fail for lack of
+// memory on a device whose pool has taken everything, and it is not free of driver-side
+// synchronisation: it belongs at start-up.  Every later call allocates nothing.
 //
 // Rules that follow from the array being shared:
 //   * capacity: M * N <= kMaxOutputs (two K-slices of fp32 partial sums always fit) and
@@ -19,7 +24,7 @@
 //     is loaded, each kernel puts them back to zero, and the first call on a device clears them again;
 //   * that first call on each device also looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and enqueues the clearing memset: make it
-//     before any stream capture begins.
+//     before the framework claims the remaining device memory and before any stream capture begins.
 #include <mutex>
 #include "afb_internal.h"
 
@@ -51,6 +56,9 @@ extern "C" int afb_gemm_launch_static(const afb_gemm_args* args, void* stream) {
     if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0 || args->flags != 0) return AFB_ERR_BAD_ARG;
     if (args->lda < args->k || args->ldc < args->n || args->ldb < args->k) return AFB_ERR_BAD_ARG;
     if (args->variant != AFB_VARIANT_AUTO && args->variant != AFB_VARIANT_DECODE) return AFB_ERR_UNSUPPORTED;
+    if (args->b_bits != 8 && args->b_bits != 4) return AFB_ERR_BAD_ARG;
+    if (args->b_encoding > 1 || args->b_layout > 1 || args->scale_dtype > 1) return AFB_ERR_BAD_ARG;
+    if ((uintptr_t)args->ptr_scale % (args->scale_dtype == AFB_SCALE_BF16 ? 2 : 4) || (uintptr_t)args->ptr_c % 2) return AFB_ERR_BAD_ARG;
     if (!decode_supports(*args)) return AFB_ERR_UNSUPPORTED;           // M <= 16, [N,K] layout, see afb_capi.h
     if ((size_t)args->m * args->n > kMaxOutputs) return AFB_ERR_TOO_LARGE;
     if (((size_t)args->n + 127) / 128 > kCounters) return AFB_ERR_TOO_LARGE;

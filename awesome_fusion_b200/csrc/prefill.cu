@@ -364,12 +364,11 @@ int launch_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
     p.status = ctx->status;
     auto kern = prefill_kernel<BITS, GROUPED, BN>;
-    static bool attr_set = false;  // per template instance
-    static int attr_dev = -1;
-    if (!attr_set || attr_dev != ctx->device) {
+    static DeviceOnce attr_set;  // per template instance
+    if (!attr_set.done(ctx->device)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
         if (e != cudaSuccess) return cuda_fail(e);
-        attr_set = true; attr_dev = ctx->device;
+        attr_set.mark(ctx->device);
     }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;

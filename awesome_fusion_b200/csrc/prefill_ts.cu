@@ -15,7 +15,7 @@
 //                         multiply by the per-channel scale (one scalar per thread), round to bf16, store C
 //   warp 1      (1 lane)  tcgen05.mma kind::f16, A from TMEM, B (activations) from shared memory,
 //                         128 x BMA x 16, fp32 accumulator in TMEM
-// One accumulator (BMA columns) + 6 weight slots (32 columns each) live in the 512 TMEM columns.
+// One accumulator (BMA columns) + 8 weight slots (32 columns each) live in the 512 TMEM columns.
 // Every wait is bounded; a wait that gives up sets the status words, all roles drain, TMEM is freed.
 #include <cstdlib>
 #include "afb_internal.h"
@@ -45,6 +45,8 @@ struct TsParams {
     uint32_t m_rot;        // row tiles are taken in rotated order, starting at this one (spreads the peers a rank pushes to)
     uint32_t group_m;      // tile order: groups of group_m row tiles; inside a group the channel tiles advance, row tile fastest
     uint32_t c_f32;
+    uint32_t exact;        // group scales only: the weight q * s goes to the tensor cores as TWO bf16 terms, hi = bf16_rn(q * s) and
+                           // lo = q * s - hi (exact: the product has at most 16 significant bits), in two TMEM slots and two MMAs
     uint32_t* tile_done;   // optional: per-tile counters, +kWorkerWarps when a tile of C has been stored (system-scope release)
     // optional (row-parallel reduce-scatter fused into the epilogue): fp32 C rows [o*push_rows, (o+1)*push_rows) go to rank o's
     // staging buffer, slot push_rank, instead of to p.c: push[o] + (push_rank * push_rows + local_row) * ldc + n
@@ -212,7 +214,9 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 }
                 ptx::tc_fence_after_sync();
                 for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
-                    if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_full_a(sa), pa, abort_flag)) {
+                    const bool two_terms = GROUPED && p.exact;   // slots sa (hi) and sa + 1 (lo) move in lockstep
+                    if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_full_a(sa), pa, abort_flag) ||
+                        (two_terms && !wait_or_abort(bar_full_a(sa + 1), pa, abort_flag))) {
                         if (!*abort_flag) { report_timeout(p.status, 23, (int)t, (int)kb); *abort_flag = 1; }
                         ok = false; break;
                     }
@@ -222,10 +226,16 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j)   // 16 k per instruction: 8 TMEM columns of weights, 32 bytes of each activation row
                         ptx::umma_bf16_ts(tmem_base, ta + 8 * j, db + 2u * j, idesc, ((kb - w.kb0) | (uint32_t)j) ? 1u : 0u);
+                    if (two_terms) {
+#pragma unroll
+                        for (int j = 0; j < BK / 16; ++j) ptx::umma_bf16_ts(tmem_base, ta + 32 + 8 * j, db + 2u * j, idesc, 1u);
+                    }
                     ptx::umma_commit(bar_empty_act(st));
                     ptx::umma_commit(bar_empty_a(sa));
+                    if (two_terms) ptx::umma_commit(bar_empty_a(sa + 1));
                     if (++st == S) { st = 0; ph ^= 1u; }
-                    if (++sa == kSlotsA) { sa = 0; pa ^= 1u; }
+                    sa += two_terms ? 2 : 1;
+                    if (sa == kSlotsA) { sa = 0; pa ^= 1u; }
                 }
                 if (ok) ptx::umma_commit(bar_acc_full);
             }
@@ -268,7 +278,9 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             if (GROUPED) sc_nxt = load_gscale(w.kb0 / kb_per_group);   // a stretch of K starts on a group boundary
             for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
                 if (GROUPED && (kb % kb_per_group) == 0) { sc_cur = sc_nxt; sc_nxt = load_gscale(kb / kb_per_group + 1); }
-                if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_empty_a(sa), pa ^ 1u, abort_flag)) {
+                const bool two_terms = GROUPED && p.exact;
+                if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_empty_a(sa), pa ^ 1u, abort_flag) ||
+                    (two_terms && !wait_or_abort(bar_empty_a(sa + 1), pa ^ 1u, abort_flag))) {
                     if (!*abort_flag) { report_timeout(p.status, 24, (int)t, (int)kb); *abort_flag = 1; }
                     ok = false; break;
                 }
@@ -297,18 +309,32 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                         o[4 * j] = qv[0]; o[4 * j + 1] = qv[1]; o[4 * j + 2] = qv[2]; o[4 * j + 3] = qv[3];
                     }
                 }
-                if (GROUPED) {
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + L::kColA + sa * 32 + kq * kOut;
+                if (two_terms) {
+                    uint32_t lo[kOut];
+#pragma unroll
+                    for (int j = 0; j < kOut; ++j) {
+                        const uint32_t hi = bf16x2_mul(o[j], sc_cur);
+                        lo[j] = bf16x2_fma(o[j], sc_cur, hi ^ 0x80008000u);   // q * s - hi: the fused product is exact, the difference fits bf16
+                        o[j] = hi;
+                    }
+                    ptx::tmem_st_cols(taddr + 32, lo);
+                } else if (GROUPED) {
 #pragma unroll
                     for (int j = 0; j < kOut; ++j) o[j] = bf16x2_mul(o[j], sc_cur);
                 }
-                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + L::kColA + sa * 32 + kq * kOut;
                 ptx::tmem_st_cols(taddr, o);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) { ptx::mbar_arrive(bar_full_a(sa)); ptx::mbar_arrive(bar_empty_raw(st)); }
+                if (lane == 0) {
+                    ptx::mbar_arrive(bar_full_a(sa));
+                    if (two_terms) ptx::mbar_arrive(bar_full_a(sa + 1));
+                    ptx::mbar_arrive(bar_empty_raw(st));
+                }
                 if (++st == S) { st = 0; ph ^= 1u; }
-                if (++sa == kSlotsA) { sa = 0; pa ^= 1u; }
+                sa += two_terms ? 2 : 1;
+                if (sa == kSlotsA) { sa = 0; pa ^= 1u; }
             }
             if (!ok) break;
             // ---- epilogue of this tile: the accumulator is complete once the last MMA has been committed ----
@@ -536,12 +562,13 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.m_tiles = (a.m + BMA - 1) / BMA;
     p.n_tiles = (a.n + BNW - 1) / BNW;
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
+    p.exact = (GROUPED && (a.flags & AFB_FLAG_GROUP_EXACT)) ? 1u : 0u;
     p.group_m = tile_done ? p.m_tiles : pick_group_m(a, p.m_tiles, p.n_tiles, BMA, ctx->sm_count);   // the exchange kernel assumes row-tile-fastest order
     p.tile_done = tile_done;
     // The tiles beyond the last full wave would keep a few SMs busy for a whole tile while the rest idle: cut each of them into
     // up to 4 stretches of K, one per CTA (up-projection shard on 8 GPUs: 448 tiles on 148 SMs = 3 waves + 4 tiles).
     p.tail_first = p.m_tiles * p.n_tiles; p.tail_tiles = 0; p.tail_parts = 0;
-    p.tail_ws = ctx->splitk_ws; p.tail_counters = ctx->splitk_counters;
+    p.tail_ws = nullptr; p.tail_counters = nullptr;
     {
         const uint32_t tiles_all = p.m_tiles * p.n_tiles, sms = (uint32_t)ctx->sm_count, nkb = a.k / BK;
         const uint32_t rest = tiles_all > sms ? tiles_all % sms : 0;
@@ -553,6 +580,10 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
             const uint32_t kb_group = GROUPED ? a.group_size / BK : 1;
             while (parts >= 2 && (nkb % parts != 0 || (nkb / parts) % kb_group != 0 || nkb / parts < 8)) --parts;
             if (parts >= 2 && (size_t)rest * parts * BMA * BNW * sizeof(float) <= ctx->splitk_ws_bytes && rest <= ctx->splitk_counter_count) {
+                int wrc = AFB_OK;
+                const DeviceCtx::Workspace* wsp = workspace_for(ctx, s, &wrc);   // this stream's own workspace
+                if (!wsp) return wrc;
+                p.tail_ws = wsp->ws; p.tail_counters = wsp->counters;
                 p.tail_first = tiles_all - rest; p.tail_tiles = rest; p.tail_parts = parts;
             }
         }
@@ -570,11 +601,11 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push[q] = (push && q < push_world) ? reinterpret_cast<float*>(push[q]) : nullptr;
     p.status = ctx->status;
     auto kern = prefill_ts_kernel<BITS, GROUPED, BMA>;
-    static int attr_dev = -1;  // per template instance
-    if (attr_dev != ctx->device) {
+    static DeviceOnce attr_set;  // per template instance
+    if (!attr_set.done(ctx->device)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
         if (e != cudaSuccess) return cuda_fail(e);
-        attr_dev = ctx->device;
+        attr_set.mark(ctx->device);
     }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;

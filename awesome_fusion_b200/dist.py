@@ -376,30 +376,48 @@ class ShardedMLP:
         return self.c_down.cpu()
 
     def e2e(self, steps=5, warmup=2):
-        """The same step through afb_gemm_host: pinned host inputs, H2D + launch + D2H inside the timed region.
-        (At N>1 the row-parallel partial sums come back to the host as this rank's fp32 partial: the exchange is
-        timed in the device-resident figure, not here.)"""
+        """The same step end to end from HOST buffers: pinned host inputs, host-to-device copies, the GEMMs, (at N > 1) the
+        exchange of the row-parallel partial sums, and the device-to-host copy of both results, all inside the timed region.
+        One GPU: through afb_gemm_host.  Several GPUs: afb_gemm_host has no exchange, so each rank copies its shards in
+        through the C ABI (afb_memcpy_h2d), runs the sharded step with the exchange, and copies its up-projection shard and
+        the complete down-projection result back (afb_memcpy_d2h)."""
         torch, lib = self.torch, self.lib
+        import time
         host = {}
         for name in ("a_up", "b_up", "s_up", "a_down", "b_down", "s_down"):
             host[name] = getattr(self, name).cpu().pin_memory()
         c_up = torch.empty((self.m, self.up_n_local), dtype=torch.bfloat16).pin_memory()
         c_down = torch.empty((self.m, self.down_n), dtype=torch.bfloat16).pin_memory()
-        a1 = lib.make_args(c_up, host["a_up"], host["b_up"], host["s_up"], self.m, self.up_n_local, self.up_k)
-        a2 = lib.make_args(c_down, host["a_down"], host["b_down"], host["s_down"], self.m, self.down_n, self.down_k_local)
         h2d = sum(host[k].numel() * host[k].element_size() for k in host)
         d2h = c_up.numel() * 2 + c_down.numel() * 2
-        import time
+        if self.world == 1:
+            a1 = lib.make_args(c_up, host["a_up"], host["b_up"], host["s_up"], self.m, self.up_n_local, self.up_k)
+            a2 = lib.make_args(c_down, host["a_down"], host["b_down"], host["s_down"], self.m, self.down_n, self.down_k_local)
+            api = "afb_gemm_host (C ABI, pinned host buffers)"
 
-        def one():
-            lib.gemm_host(a1)
-            lib.gemm_host(a2)
+            def one():
+                lib.gemm_host(a1)
+                lib.gemm_host(a2)
+        else:
+            stream = torch.cuda.current_stream().cuda_stream
+            c_down_dev = self.px.c if self.px is not None else self.c_down.data_ptr()
+            api = "afb_memcpy_h2d + sharded GEMMs + exchange + afb_memcpy_d2h (C ABI, pinned host buffers)"
+
+            def one():
+                for name in host:
+                    lib.h2d(getattr(self, name).data_ptr(), host[name].data_ptr(), host[name].numel() * host[name].element_size())
+                self.step(stream)
+                torch.cuda.current_stream().synchronize()
+                lib.d2h(c_up.data_ptr(), self.c_up.data_ptr(), c_up.numel() * 2)
+                lib.d2h(c_down.data_ptr(), c_down_dev, c_down.numel() * 2)
         for _ in range(warmup):
             one()
         torch.cuda.synchronize()
+        if self.world > 1:
+            self.tdist.barrier()
         t0 = time.perf_counter()
         for _ in range(steps):
             one()
         torch.cuda.synchronize()
         ms = (time.perf_counter() - t0) / steps * 1e3
-        return {"ms": ms, "h2d": h2d, "d2h": d2h}
+        return {"ms": ms, "h2d": h2d, "d2h": d2h, "api": api}

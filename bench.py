@@ -29,11 +29,12 @@ sys.path.insert(0, ROOT)
 
 METRIC = "bf16 x int GEMM throughput (2*M*N*K / time)"
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the up-projection on one GPU (ncu capture summarised in
-# profiles/launch_list_bench_n1.md): 634.0 MB + 223.4 MB
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the up-projection kernel on one GPU, from an ncu capture of
+# that kernel on that shape (a profiler figure cannot be taken inside a timed run): 634.0 MB + 223.4 MB
 UP_PROJ_DRAM_BYTES = 633972736 + 223373568
-# same for the decode kernel, int8 M=16 at 4096 x 4096 (profiles/decode_kernel_int8_m16_4096x4096.md)
+# same for the decode kernel, int8 M=16 at 4096 x 4096
 DECODE_M16_DRAM_BYTES = 16940800
+PARITY_ROWS = [0, 255, 256, 1000, 2047, 2048, 3583, 4095]   # activation rows of both GEMMs checked against the CPU oracle after the timed region
 FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -270,6 +271,48 @@ def run_reference_arm(args):
     return 0
 
 
+def parity_check(mlp, torch, world, rank):
+    """After the timed region: PARITY_ROWS of the up-projection (this rank's channels) and of the down-projection (the
+    complete sum, as this rank holds it after the exchange) against the CPU oracle on the same inputs.  For the K-split
+    GEMM every rank computes the oracle's fp32 partial rows of its own K range and the ranks add them up.
+    Returns the worst figures over the ranks.  The oracle is only the checker here: nothing timed runs through it."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import afb_testlib as T
+    oracle = T.load_oracle()
+    rows = [r for r in PARITY_ROWS if r < mlp.m]
+    threads = max(1, (os.cpu_count() or 1) // max(1, world))
+
+    def to_u16(t):
+        return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def case_of(a, b, s):
+        n, k = b.shape
+        return T.Case(m=len(rows), n=n, k=k, bits=8, group=0, layout=1, enc=0, scale_dtype=0, a=to_u16(a[rows]),
+                      b=b.cpu().numpy().view(np.uint8), scale=s.cpu().numpy().astype(np.float32), ldb=k)
+
+    worst, worst_nrms = 0.0, 0.0
+    # column-parallel up-projection: this rank's channels
+    ref = oracle.gemm(case_of(mlp.a_up, mlp.b_up, mlp.s_up), threads=threads)
+    mx, nrms, _ = oracle.compare(ref, to_u16(mlp.c_up[rows]), T.rms(ref) * 0.05)
+    worst, worst_nrms = max(worst, mx), max(worst_nrms, nrms)
+    # row-parallel down-projection: oracle partial sums of this rank's K range, added over the ranks
+    part = torch.from_numpy(oracle.gemm(case_of(mlp.a_down, mlp.b_down, mlp.s_down), threads=threads)).cuda()
+    if world > 1:
+        import torch.distributed as tdist
+        tdist.all_reduce(part)
+    ref = part.cpu().numpy()
+    got = mlp.result_down()[rows].contiguous().view(torch.int16).numpy().view(np.uint16)
+    mx, nrms, _ = oracle.compare(ref, got, T.rms(ref) * 0.05)
+    worst, worst_nrms = max(worst, mx), max(worst_nrms, nrms)
+    t = torch.tensor([worst, worst_nrms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+    worst, worst_nrms = t[0].item(), t[1].item()
+    return {"rows": rows, "gemms": ["up (each rank's channels)", "down (complete sum on every rank)"], "max_rel": worst, "nrms": worst_nrms,
+            "tolerance": 1e-2, "floor": "0.05 x RMS(ref)", "checked_on_ranks": world, "ok": bool(worst <= 1e-2)}
+
+
 def headline_config(n_gpus):
     return {"workload": "sharded-mlp: column-parallel up-proj 4096 x 28672 x 8192 + row-parallel down-proj 4096 x 8192 x 28672, "
                         "int8 weights [N,K], per-channel fp32 scales, bf16 in/out, fp32 accumulate",
@@ -350,11 +393,12 @@ def run_ours(args):
         tdist.all_reduce(t2, op=tdist.ReduceOp.MAX)
         e2e["ms"] = t2.item()
     e2e_obj = {"value": total_flops / e2e["ms"] / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d"] * world,
-               "d2h_bytes_per_step": e2e["d2h"] * world, "ms_per_step": e2e["ms"], "api": "afb_gemm_host (C ABI, pinned host buffers)"}
+               "d2h_bytes_per_step": e2e["d2h"] * world, "ms_per_step": e2e["ms"], "api": e2e["api"]}
 
+    parity = parity_check(mlp, torch, world, rank)
     shutdown(mlp, world, torch)
     if rank != 0:
-        return 0
+        return 0 if parity["ok"] else 1
     # roofline of the dominant kernel (the prefill kernel of the up-projection: no exchange inside its events)
     up_flops = gemm_flops(mlp.m, mlp.up_n_local, mlp.up_k)
     achieved = up_flops / up_ms / 1e9
@@ -362,12 +406,12 @@ def run_ours(args):
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                 "peak_source": f"{peaks['_source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
                 "frac_of_nominal": achieved / NOMINAL["bf16_tflops"], "avg_launch_ms": up_ms,
-                "traffic": UP_PROJ_DRAM_BYTES if world == 1 else None, "traffic_source": "profiles/launch_list_bench_n1.md" if world == 1 else None,
+                "traffic": UP_PROJ_DRAM_BYTES if world == 1 else None, "traffic_source": "ncu capture of this kernel on this shape" if world == 1 else None,
                 "algorithmic_bytes": gemm_bytes(mlp.m, mlp.up_n_local, mlp.up_k, 8, 0)}
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint8->fp32", "data": "synthetic",
-            "config": {**headline_config(world), "exchange": mlp.exchange_name}, "clocks": clocks, "e2e": e2e_obj, "gpu_launches": launches,
-            "roofline": roofline, "per_gemm_ms": {"up": up_ms, "down_incl_exchange": down_ms}, "device_status": status}
+            "config": headline_config(world), "exchange": mlp.exchange_name, "clocks": clocks, "e2e": e2e_obj, "gpu_launches": launches,
+            "roofline": roofline, "per_gemm_ms": {"up": up_ms, "down_incl_exchange": down_ms}, "device_status": status, "parity": parity}
     if world == 1:
         cases = []
         if not args.no_cases:
@@ -378,12 +422,12 @@ def run_ours(args):
             d16 = next(c for c in cases if c["name"] == "decode-m16")
             line["roofline_decode"] = {"kernel": "decode_kernel<8,2,false>", "bound": "hbm", "achieved": d16["gbs"], "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": d16["gbs"] / peaks["hbm_gbs"], "peak_source": f"{peaks['_source']} copy bandwidth",
-                                       "traffic": DECODE_M16_DRAM_BYTES, "traffic_source": "profiles/decode_kernel_int8_m16_4096x4096.md"}
+                                       "traffic": DECODE_M16_DRAM_BYTES, "traffic_source": "ncu capture of this kernel on this shape"}
         if not args.no_cpu:
             v, info, _ = cpu_arm()
             line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}
     print(json.dumps(line))
-    return 0
+    return 0 if parity["ok"] and status[0] == 0 else 1
 
 
 def shutdown(mlp, world, torch):

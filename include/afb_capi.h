@@ -53,6 +53,13 @@ extern "C" {
 #define AFB_FLAG_PUSH_VIA_LOCAL 8u /* afb_gemm_launch_push only: ptr_c is a local fp32 [M,N] scratch (ldc = N); the epilogue stores there and two
                                       extra warps per CTA forward each finished tile to its owner while the next tile is computed */
 
+#define AFB_FLAG_GROUP_EXACT 32u /* prefill variant with per-group scales: feed each weight q * s to the tensor cores as two bf16 terms
+                                   (hi = bf16_rn(q * s), lo = q * s - hi, exact) instead of the one rounded term: twice the tensor-core
+                                   work, and the result is that of the fp32 formula of host_ref.hpp:15-24 up to summation order.
+                                   No effect where the scale never touches the weights (per-channel scales, decode variant). */
+#define AFB_FLAG_DUMP_DECODE_PAIRING 16u /* afb_dequant_dump only ([N,K] layout): unpack with the decode kernel's routines (strided pairing,
+                                         integer values, no scale) instead of the prefill kernel's; the output is in natural k order either way */
+
 /*
  * Kernel argument block.  The first ten fields are the reference's packed kernarg
  * block, same order and types (bfAintBGemm.cc:119-133; bf16gemm_kernel_gfx90a.s:97-108).
@@ -110,9 +117,11 @@ int afb_device_sync(void);
 /* hipModuleLaunchKernel (bfAintBGemm.cc:152,176): validates args, picks the variant,
  * decides grid/block/shared memory/tensor maps itself and launches asynchronously on
  * `stream` (NULL = the default stream).  Pointers are DEVICE pointers.
- * GEMMs that split K between CTAs (decode K-slices, short last wave of prefill tiles) use
- * the context's fp32 workspace: two launches on one device must not overlap on the GPU
- * (one stream per device serialises them).                                             */
+ * GEMMs that split K between CTAs (decode K-slices, short last wave of prefill tiles) meet in an
+ * fp32 workspace that belongs to the STREAM they are launched on: launches on one stream are
+ * serialised by the stream, launches on different streams use different workspaces.  A stream's
+ * workspace (32 MiB) is allocated on its first such launch, which therefore must not happen inside
+ * a stream capture; at most 16 streams per device, after that AFB_ERR_TOO_LARGE.            */
 int afb_gemm_launch(const afb_gemm_args* args, void* stream);
 /* Which variant AFB_VARIANT_AUTO resolves to for these args (no launch). */
 int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
@@ -122,11 +131,16 @@ int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
 int afb_gemm_host(const afb_gemm_args* host_args, void* stream);
 /* No counterpart in the reference.  The decode GEMM (M <= 16, B in [N,K] layout) for callers that must not
  * allocate: programs whose framework already owns all device memory, and latency-critical loops that cannot
- * afford the device-wide synchronisation of cudaMalloc.  Needs no afb_init and calls no allocator: its split-K
- * scratch is a fixed array inside the library (about 4 MiB held on every GPU that loads libafb.so).
+ * afford the device-wide synchronisation of cudaMalloc.  Needs no afb_init and calls no cudaMalloc / cudaFree or
+ * other allocating routine: its split-K scratch is a fixed array inside the library image (about 4 MiB).
  * Limits: M * N <= 524288 and N <= 524288, else AFB_ERR_TOO_LARGE.  All calls on a device share the array:
- * calls that overlap on the GPU race, so keep them on one stream.  The first call on each device does a
- * one-time set-up (address look-up and a clearing memset on `stream`): make it before any stream capture. */
+ * calls that overlap on the GPU race, so keep them on one stream.
+ * The first call on each device is the set-up call: it looks up the array's device address and enqueues a
+ * clearing memset on `stream`.  With CUDA's default lazy module loading that first call is also the moment the
+ * driver places this library's image -- the array and the kernel code -- in device memory, so it is not free of
+ * driver-side allocation or synchronisation: make it once per device at start-up, before the host framework
+ * takes the rest of the memory and before any stream capture (or run with CUDA_MODULE_LOADING=EAGER).  From
+ * the second call on, nothing is allocated by anyone. */
 int afb_gemm_launch_static(const afb_gemm_args* args, void* stream);
 /* Dequantised weights exactly as the kernels feed them to the tensor cores:
  * out is bf16 with B's logical shape and layout ([N,K] ld=K for COL, [K,N] ld=N for ROW).

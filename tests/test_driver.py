@@ -30,6 +30,8 @@ def test_driver_builds_and_rejects_bad_options():
     (["1", "16", "4096", "4096", "b_layout=col", "enc=twos", "data=real"], "decode"),
     (["1", "4", "1024", "2048", "b_layout=col", "bits=4", "group=128", "data=real"], "decode"),
     (["1", "160", "512", "1024", "b_layout=col", "bits=4", "group=128", "data=real", "enc=twos"], "prefill"),
+    (["1", "160", "512", "1024", "b_layout=col", "bits=4", "group=128", "data=real", "enc=twos", "exact=1"], "prefill"),   # two-term mode: the 1e-2 contract
+    (["1", "256", "1024", "1024", "b_layout=col", "enc=twos", "data=real", "a_dist=uniform", "scale_lo=0.002", "scale_hi=0.02", "seed=0"], "prefill"),
     (["1", "33", "136", "192", "300", "136", "200"], "naive"),               # explicit leading dimensions
 ])
 def test_driver_validation_mode(argv, variant):

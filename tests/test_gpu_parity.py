@@ -14,6 +14,9 @@ GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 TOL = 1e-2            # max relative error on bf16 outputs
 FLOOR_FRAC = 0.05     # |ref| below this fraction of RMS(ref) is compared against the floor instead
+# Group-scaled prefill in its default (one rounded bf16 term per weight) mode against the pure-fp32 formula, at the same floor:
+# the documented exception to the 1e-2 contract (AFB_FLAG_GROUP_EXACT is the mode that meets it).
+GROUPED_ONE_TERM_BOUND = 0.25
 
 
 def check_close(oracle, ref, got_bf16, what, tol=TOL, floor_frac=FLOOR_FRAC):
@@ -60,6 +63,24 @@ def test_dequant_groups_and_int4(afb, oracle, bits, group, enc, scale_dtype):
     if group and scale_dtype == 0:
         # fp32 scales are first rounded to bf16 by the kernels (the dequant contract multiplies two bf16 values)
         case.scale = T.np_bf16_rne(case.scale); case.scale_dtype = 1
+    assert np.array_equal(got, oracle.dequant_bf16(case))
+
+
+@pytest.mark.parametrize("bits,enc", [(8, 0), (8, 1), (4, 0), (4, 1)])
+def test_dequant_decode_pairing_is_bit_exact(afb, oracle, bits, enc):
+    """The decode kernel unpacks with the strided pairing ({k0,k2},{k1,k3} for int8, {k0,k4}..{k3,k7} for int4).  The dump runs
+    those same device routines and stores the values back in natural k order: every byte value, both encodings."""
+    n, k = 64, 512
+    raw = (np.arange(n * k * bits // 8, dtype=np.uint32) * 7 + 3).astype(np.uint8).reshape(n, k * bits // 8)   # every byte value, many times
+    case = T.Case(m=1, n=n, k=k, bits=bits, group=0, layout=1, enc=enc, scale_dtype=0, b=raw, scale=np.ones(n, np.float32), ldb=k)
+    d_b, d_s = afb.to_device(case.b), afb.to_device(case.scale)
+    d_o = afb.malloc(n * k * 2)
+    args = afb.make_args(d_o, d_b, d_b, d_s, 1, n, k, ldb=k, bits=bits, encoding=enc, layout=1, flags=pkg.FLAG_DUMP_DECODE_PAIRING)
+    afb.dequant_dump(args, d_o)
+    afb.device_sync()
+    got = afb.to_host(d_o, (n, k), np.uint16)
+    for p in (d_b, d_s, d_o):
+        afb.free(p)
     assert np.array_equal(got, oracle.dequant_bf16(case))
 
 
@@ -136,14 +157,18 @@ def test_prefill_int4_and_groups(afb, oracle, m, n, k, bits, group, scale_dtype,
     got, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=impl)
     ref_exact = oracle.gemm(case, threads=8)
     if group:
-        # tight check against the oracle fed with the SAME bf16-rounded weights the tensor cores see ...
+        # Tensor-core operands are bf16, so by default a per-group scale is folded into the weight before the MMA:
+        # w = bf16_rn(q * s) carries a relative error of up to 2^-9 per weight that the fp32 formula of host_ref.hpp:15-24
+        # does not have.  Tight check against the oracle fed with the SAME rounded weights ...
         check_close(oracle, oracle.gemm(case, round_w=True, threads=8), got, f"prefill int{bits} g{group} (rounded-weight oracle)")
-        # ... and the check against the pure-fp32 formula of host_ref.hpp:15-24.  Tensor-core operands are bf16, so a
-        # per-group scale has to be folded into the weight before the MMA: w = bf16_rn(q * s) carries a relative error of
-        # up to 2^-9 per weight, which the fp32 formula does not have.  Measured: NRMS 1.6e-3, worst element 1.13e-2 of
-        # max(|ref|, RMS) -- the one place above 1e-2; the bound here is 1.5e-2 and the NRMS bound 3e-3.
-        mx, nrms = check_close(oracle, ref_exact, got, f"prefill int{bits} g{group} (host_ref formula)", tol=1.5e-2, floor_frac=1.0)
-        assert nrms < 3e-3
+        # ... and the deviation from the pure-fp32 formula, at the standard floor, stated as what it is (it does not meet 1e-2):
+        mx, nrms, _ = oracle.compare(ref_exact, got, T.rms(ref_exact) * FLOOR_FRAC)
+        print(f"group-scaled prefill, one rounded term: max rel err {mx:.3e} at the 0.05 x RMS floor, nrms {nrms:.3e}")
+        assert nrms < 3e-3 and mx < GROUPED_ONE_TERM_BOUND
+        # AFB_FLAG_GROUP_EXACT feeds q * s as two bf16 terms (exact): this mode meets the 1e-2 contract against host_ref
+        if impl == pkg.FLAG_PREFILL_TMEM_A:
+            exact, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=impl | pkg.FLAG_GROUP_EXACT)
+            check_close(oracle, ref_exact, exact, f"prefill int{bits} g{group} two-term mode (host_ref formula)")
     else:
         check_close(oracle, ref_exact, got, f"prefill int{bits} {m}x{n}x{k}")
     assert afb.read_status()[0] == 0
@@ -359,9 +384,13 @@ def test_prefill_tail_tiles_split_along_k(afb, oracle, monkeypatch, bits, group,
         assert np.abs(a - ref).max() <= 2e-3 * T.rms(ref) + tol and np.abs(whole - ref).max() <= 2e-3 * T.rms(ref) + tol
         assert not np.array_equal(a[:, -256:], np.zeros_like(a[:, -256:]))
     else:
-        grouped = group != 0
-        check_close(oracle, ref, a, "tail split", tol=1.5e-2 if grouped else TOL, floor_frac=1.0 if grouped else FLOOR_FRAC)
-        check_close(oracle, ref, whole, "no tail split", tol=1.5e-2 if grouped else TOL, floor_frac=1.0 if grouped else FLOOR_FRAC)
+        if group:   # one rounded term per weight: tight against the oracle fed with the same rounded weights
+            ref = oracle.gemm(case, threads=8, round_w=True)
+        check_close(oracle, ref, a, "tail split")
+        check_close(oracle, ref, whole, "no tail split")
+        if group:   # the two-term mode through the tail split, against the fp32 formula
+            ex, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags | pkg.FLAG_GROUP_EXACT)
+            check_close(oracle, oracle.gemm(case, threads=8), ex, "tail split, two-term mode")
     # the split only changes the order of the fp32 additions of the two tail tiles: everything else is bit-identical
     same = np.mean(a == whole)
     assert same > 0.97, same

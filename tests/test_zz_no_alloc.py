@@ -49,6 +49,46 @@ def test_static_scratch_entry_matches_regular_entry(m, n, k, bits, group):
     assert mx <= 1e-2
 
 
+@pytest.mark.parametrize("env", [{"AFB_DECODE_SLICES": "2", "AFB_DECODE_WR": "8"}, {"AFB_DECODE_SLICES": "4", "AFB_DECODE_WR": "8"},
+                                 {"AFB_DECODE_BALANCED": "1"}])
+def test_static_scratch_at_the_capacity_edge_and_free_memory_unchanged(monkeypatch, env):
+    """M * N = 524288 is the largest problem the fixed array takes: exactly two K-slices of fp32 partial sums fit.  The
+    launch shape is forced to use them (two slices: fits; four slices and the balanced form with more than two sharing
+    CTAs: do not fit, and the launcher must fall back to a shape that does, not overrun the array).  Around the later
+    calls the device's free memory must not move: that is the property the entry point is named for."""
+    import torch
+    lib = pkg.load()
+    m, n, k = 16, 32768, 1024
+    case = T.make_case(m, n, k, seed=23)
+    dc = T.DeviceCase(lib, case, guard=4096)
+    try:
+        for name, val in env.items():
+            monkeypatch.setenv(name, val)
+        lib.memset(dc.d_c_base, 0xCD, dc.c_bytes + 2 * 4096)
+        assert lib.gemm_launch_static_status(dc.args()) == 0          # set-up call for this process, if none came before
+        lib.device_sync()
+        first, raw = dc.result()
+        free_before = torch.cuda.mem_get_info(0)[0]
+        assert lib.gemm_launch_static_status(dc.args()) == 0
+        lib.device_sync()
+        free_after = torch.cuda.mem_get_info(0)[0]
+        second, raw = dc.result()
+        for name in env:
+            monkeypatch.delenv(name)
+        lib.init(0)
+        lib.gemm_launch(dc.args(variant=pkg.VARIANT_DECODE))
+        lib.device_sync()
+        regular = dc.result()[0]
+    finally:
+        dc.close()
+    assert free_after == free_before, f"free device memory moved by {free_before - free_after} bytes across a call"
+    assert np.array_equal(first, second)
+    assert np.all(raw[:4096] == 0xCD) and np.all(raw[-4096:] == 0xCD)
+    ref = T.np_bf16_to_f32(regular)
+    mx, _, worst = T.load_oracle().compare(ref, first, T.rms(ref) * 0.05)
+    assert mx <= 1e-2, f"static entry differs from the regular entry: {mx} at {worst}"
+
+
 def test_static_scratch_entry_refuses_what_does_not_fit():
     lib = pkg.load()
     # 16 x 40960 outputs exceed the 524288-output capacity; prefill-sized M has no static variant
