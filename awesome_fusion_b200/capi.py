@@ -10,7 +10,7 @@ import os
 import numpy as np
 
 ENC_TWOS, ENC_OFFSET = 0, 1
-LAYOUT_ROW, LAYOUT_COL = 0, 1
+LAYOUT_ROW, LAYOUT_COL, LAYOUT_COL_PACKED = 0, 1, 2
 SCALE_F32, SCALE_BF16 = 0, 1
 VARIANT_AUTO, VARIANT_DECODE, VARIANT_PREFILL, VARIANT_NAIVE = 0, 1, 2, 3
 FLAG_C_F32 = 1
@@ -19,6 +19,7 @@ FLAG_PREFILL_TMEM_A = 4
 FLAG_PUSH_VIA_LOCAL = 8
 FLAG_DUMP_DECODE_PAIRING = 16
 FLAG_GROUP_EXACT = 32
+FLAG_PDL = 64
 IPC_HANDLE_BYTES = 64
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -29,7 +30,7 @@ EXPORTS = [
     "afb_free_host", "afb_memcpy_h2d", "afb_memcpy_d2h", "afb_memcpy_d2d", "afb_memset", "afb_event_create",
     "afb_event_record", "afb_event_sync", "afb_event_elapsed_ms", "afb_event_destroy", "afb_stream_create",
     "afb_stream_sync", "afb_stream_destroy", "afb_device_sync", "afb_gemm_launch", "afb_gemm_resolve_variant",
-    "afb_gemm_host", "afb_gemm_launch_static", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
+    "afb_gemm_host", "afb_gemm_launch_static", "afb_prepack", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
     "afb_ksplit_allreduce_launch", "afb_cast_f32_to_bf16", "afb_ksplit_tile_info", "afb_gemm_launch_tiles", "afb_ksplit_tile_allreduce_launch", "afb_gemm_launch_push", "afb_abi_sizes",
     "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
 ]
@@ -103,6 +104,7 @@ class Library:
         L.afb_gemm_host.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_gemm_launch_static.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_dequant_dump.argtypes = [ctypes.POINTER(GemmArgs), vp, vp]
+        L.afb_prepack.argtypes = [ctypes.POINTER(GemmArgs), vp, ctypes.c_uint32, vp]
         L.afb_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
         L.afb_ipc_export.argtypes = [vp, ctypes.c_char_p]
         L.afb_ipc_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
@@ -226,7 +228,7 @@ class Library:
         args.ptr_c, args.ptr_a, args.ptr_b, args.ptr_scale = _ptr(c), _ptr(a), _ptr(b), _ptr(scale)
         args.m, args.n, args.k = m, n, k
         args.lda = k if lda is None else lda
-        args.ldb = (k if layout == LAYOUT_COL else n) if ldb is None else ldb
+        args.ldb = (n if layout == LAYOUT_ROW else k) if ldb is None else ldb
         args.ldc = n if ldc is None else ldc
         args.b_bits, args.b_encoding, args.b_layout = bits, encoding, layout
         args.scale_dtype, args.group_size, args.variant, args.flags, args.reserved = scale_dtype, group, variant, flags, 0
@@ -249,6 +251,10 @@ class Library:
         v = ctypes.c_uint32(0)
         self.check(self.lib.afb_gemm_resolve_variant(ctypes.byref(args), ctypes.byref(v)), "afb_gemm_resolve_variant")
         return v.value
+
+    def prepack(self, args, out_b, out_ldb, stream=None):
+        """afb_prepack: B of `args` ([K,N] or [N,K]) -> the pre-packed [N,K] layout in `out_b`."""
+        self.check(self.lib.afb_prepack(ctypes.byref(args), _ptr(out_b), out_ldb, stream), "afb_prepack")
 
     def dequant_dump(self, args, out, stream=None):
         self.check(self.lib.afb_dequant_dump(ctypes.byref(args), _ptr(out), stream), "afb_dequant_dump")

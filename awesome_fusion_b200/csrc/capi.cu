@@ -77,12 +77,13 @@ static int validate(const afb_gemm_args* a) {
     if (a->m == 0 || a->n == 0 || a->k == 0) return AFB_ERR_BAD_ARG;
     if (a->reserved != 0) return AFB_ERR_BAD_ARG;
     if (a->b_bits != 8 && a->b_bits != 4) return AFB_ERR_BAD_ARG;
-    if (a->b_encoding > 1 || a->b_layout > 1 || a->scale_dtype > 1 || a->variant > 3) return AFB_ERR_BAD_ARG;
+    if (a->b_encoding > 1 || a->b_layout > 2 || a->scale_dtype > 1 || a->variant > 3) return AFB_ERR_BAD_ARG;
     if (a->flags & ~(AFB_FLAG_C_F32 | AFB_FLAG_PREFILL_SMEM_B | AFB_FLAG_PREFILL_TMEM_A | AFB_FLAG_GROUP_EXACT)) return AFB_ERR_BAD_ARG;
     if ((a->flags & AFB_FLAG_GROUP_EXACT) && (a->flags & AFB_FLAG_PREFILL_SMEM_B) && a->group_size) return AFB_ERR_UNSUPPORTED;   // only the tensor-memory form has it
     if (a->lda < a->k || a->ldc < a->n) return AFB_ERR_BAD_ARG;
-    if (a->b_layout == AFB_LAYOUT_COL ? a->ldb < a->k : a->ldb < a->n) return AFB_ERR_BAD_ARG;
-    if (a->b_bits == 4 && (a->b_layout != AFB_LAYOUT_COL || (a->k & 1) || (a->ldb & 1))) return AFB_ERR_UNSUPPORTED;
+    if (a->b_layout != AFB_LAYOUT_ROW ? a->ldb < a->k : a->ldb < a->n) return AFB_ERR_BAD_ARG;
+    if (a->b_bits == 4 && (a->b_layout == AFB_LAYOUT_ROW || (a->k & 1) || (a->ldb & 1))) return AFB_ERR_UNSUPPORTED;
+    if (a->b_layout == AFB_LAYOUT_COL_PACKED && a->k % (a->b_bits == 8 ? 4u : 8u)) return AFB_ERR_BAD_ARG;   // whole words
     if (a->group_size && (a->k % a->group_size)) return AFB_ERR_BAD_ARG;
     // element alignment of what the kernels load and store as 2- or 4-byte words (a misaligned pointer would fault on the GPU)
     if ((uintptr_t)a->ptr_scale % (a->scale_dtype == AFB_SCALE_BF16 ? 2 : 4)) return AFB_ERR_BAD_ARG;
@@ -265,8 +266,8 @@ int afb_gemm_launch(const afb_gemm_args* args, void* stream) {
 
 static size_t b_bytes(const afb_gemm_args& a) {
     const size_t ld_bytes = (size_t)a.ldb * a.b_bits / 8;
-    const size_t rows = a.b_layout == AFB_LAYOUT_COL ? a.n : a.k;
-    const size_t cols_bytes = (size_t)(a.b_layout == AFB_LAYOUT_COL ? a.k : a.n) * a.b_bits / 8;
+    const size_t rows = a.b_layout != AFB_LAYOUT_ROW ? a.n : a.k;
+    const size_t cols_bytes = (size_t)(a.b_layout != AFB_LAYOUT_ROW ? a.k : a.n) * a.b_bits / 8;
     return (rows - 1) * ld_bytes + cols_bytes;  // the size rule of bfAintBGemm.cc:68-76
 }
 
@@ -295,7 +296,7 @@ int afb_gemm_host(const afb_gemm_args* h, void* stream) {
     // Pipelined form for B in [N,K] layout with per-channel scales: the channels are cut into chunks; while chunk i is
     // multiplied, chunk i+1 of the weights travels host -> device and chunk i-1 of C travels device -> host (PCIe is full duplex).
     constexpr uint32_t kChunks = 8;
-    const bool pipelined = h->b_layout == AFB_LAYOUT_COL && h->group_size == 0 && h->m > 16 && h->n >= kChunks * 512 && h->n % (kChunks * 128) == 0;
+    const bool pipelined = h->b_layout != AFB_LAYOUT_ROW && h->group_size == 0 && h->m > 16 && h->n >= kChunks * 512 && h->n % (kChunks * 128) == 0;
     if (!pipelined) {
         AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, s));
         AFB_CUDA(cudaMemcpyAsync(ctx->stage[2], h->ptr_b, need[2], cudaMemcpyHostToDevice, s));
@@ -350,7 +351,8 @@ int afb_dequant_dump(const afb_gemm_args* args, void* out_bf16, void* stream) {
     if (!args || !args->ptr_b || !out_bf16 || args->n == 0 || args->k == 0) return AFB_ERR_BAD_ARG;
     if (args->b_bits != 8 && args->b_bits != 4) return AFB_ERR_BAD_ARG;
     if (args->group_size && !args->ptr_scale) return AFB_ERR_BAD_ARG;
-    if (args->b_bits == 4 && args->b_layout != AFB_LAYOUT_COL) return AFB_ERR_UNSUPPORTED;
+    if (args->b_bits == 4 && args->b_layout == AFB_LAYOUT_ROW) return AFB_ERR_UNSUPPORTED;
+    if (args->b_layout > 2) return AFB_ERR_BAD_ARG;
     if (!current_ctx()) return AFB_ERR_NOT_INIT;
     return launch_dequant_dump(*args, out_bf16, (cudaStream_t)stream);
 }

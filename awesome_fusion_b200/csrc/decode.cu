@@ -23,13 +23,12 @@
 #include <cstdlib>
 #include "afb_internal.h"
 #include "dequant.cuh"
+#include "decode_common.cuh"
 
 namespace afb {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = 8;
 #ifndef AFB_DECODE_RING
 #define AFB_DECODE_RING 4
 #endif
@@ -40,9 +39,7 @@ constexpr int kWarps = 8;
 #define AFB_DECODE_MT2_CTAS 3
 #endif
 constexpr int kRing = AFB_DECODE_RING;         // cp.async stages per warp (power of two)
-constexpr int kStageBytes = 1024;              // 2 channels x 32 lanes x 16 bytes
 constexpr int kRingBytes = kWarps * kRing * kStageBytes;   // 32 KiB
-constexpr int kRedFloats = kWarps * 16 * 17;   // cross-warp reduction buffer, [warp][16 channels][<=16 rows + pad]; reuses the ring once the stream has ended
 // staged activations of one pass, m rows x (pass_k * 2 + 16) bytes: 20 KiB for m <= 8 (52 KiB per CTA: four CTAs per SM, 64 registers),
 // 40 KiB for m <= 16 (72 KiB per CTA: three CTAs per SM, 80 registers)
 __host__ __device__ constexpr int act_bytes(int mt) { return mt == 1 ? 20 * 1024 : 40 * 1024; }
@@ -50,55 +47,6 @@ constexpr int kOffRed = 0;
 constexpr int kOffAct = kRingBytes;
 __host__ __device__ constexpr int smem_bytes(int mt) { return kOffAct + act_bytes(mt) + 16; }
 static_assert(kRedFloats * 4 <= kRingBytes, "the reduction buffer must fit the ring it reuses");
-
-struct DecodeParams {
-    const uint16_t* a;
-    const uint8_t* b;
-    const void* scale;
-    uint16_t* c;
-    uint32_t m, n, k, lda, ldb_bytes, ldc;
-    uint32_t enc, scale_dtype, group;
-    uint32_t wr;      // warps along the channel dimension (1, 2, 4 or 8); WK = 8 / wr
-    uint32_t kc;      // k elements per slice (multiple of the chunk)
-    uint32_t pass_k;  // k elements staged per pass (multiple of chunk * WK; m * (pass_k * 2 + 16) <= act_bytes)
-    uint32_t group_shift;  // log2(group) (groups are powers of two)
-    uint32_t slices;  // gridDim.y
-    // balanced form (streamk = 1): the grid is one wave of CTAs; the weights are cut into units of 16*wr channels x unit_k
-    // elements of K, numbered channel block major, and CTA c takes units [c*U/G, (c+1)*U/G): whole runs of K of one or more
-    // channel blocks.  A channel block shared by several CTAs is finished by the last of them to arrive, in CTA order.
-    uint32_t streamk, unit_k, units_per_cb, total_units;
-    float* ws;        // [contributor][m][n] fp32 partial sums (K-slices, or the CTAs sharing a channel block)
-    uint32_t* counters;  // one per channel block, zero on entry, zero again on exit
-};
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 ldg_act(const uint16_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ float bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
-__device__ __forceinline__ float load_scale(const void* s, size_t idx, uint32_t dtype) {
-    return dtype == AFB_SCALE_BF16 ? bf16_to_f32(reinterpret_cast<const uint16_t*>(s)[idx]) : reinterpret_cast<const float*>(s)[idx];
-}
-
-__device__ __forceinline__ uint32_t swz_piece(uint32_t pc) { return pc ^ (((pc >> 3) & 1u) << 1); }
 
 template <int BITS, int MT, bool GROUPED>
 // resident CTAs per SM the register budget is cut for: the group-scaled int4 kernels want more registers than the others (16 rows:
@@ -287,59 +235,7 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
             s_red[(warp * 16 + (e < 2 ? g : g + 8)) * 17 + mt * 8 + 2 * tig + (e & 1)] = acc[mt][e];
     __syncthreads();
 
-    const uint32_t rows_cta = 16 * p.wr;
-    const uint32_t outputs = rows_cta * MCOLS;          // <= 2048
-    uint32_t contributors = p.slices, my_slot = blockIdx.y;
-    if (p.streamk) {   // the CTAs whose runs of units touch this channel block, in CTA order (= ascending K)
-        const uint32_t first = cta_of(cb * p.units_per_cb), last = cta_of(cb * p.units_per_cb + p.units_per_cb - 1);
-        contributors = last - first + 1; my_slot = blockIdx.x - first;
-    }
-    const bool single = contributors == 1;
-    for (uint32_t idx = tid; idx < outputs; idx += kThreads) {
-        const uint32_t mm = idx / rows_cta, r = idx - mm * rows_cta;   // consecutive threads -> consecutive channels
-        const uint32_t nn = nblk + r;
-        if (mm >= p.m || nn >= p.n) continue;
-        const uint32_t w0 = (r >> 4) * wk_count;
-        float sum = 0.f;
-        for (uint32_t w = 0; w < wk_count; ++w) sum += s_red[((w0 + w) * 16 + (r & 15)) * 17 + mm];
-        if (single) {
-            if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
-            p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
-        } else {
-            __stcg(p.ws + ((size_t)my_slot * p.m + mm) * p.n + nn, sum);
-        }
-    }
-    if (!single) {
-        // several contributors (K-slices, or CTAs sharing the channel block): the last to arrive adds the published partial
-        // sums in contributor order (= ascending K), so the result does not depend on who that is
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const uint32_t old = atomicAdd(p.counters + cb, 1u);
-            *s_last = (old == contributors - 1) ? 1u : 0u;
-        }
-        __syncthreads();
-        if (*s_last) {
-            __threadfence();
-            for (uint32_t idx = tid; idx < p.m * rows_cta; idx += kThreads) {
-                const uint32_t mm = idx / rows_cta, nn = nblk + (idx % rows_cta);
-                if (nn >= p.n) continue;
-                const float* src = p.ws + (size_t)mm * p.n + nn;
-                const size_t slice_stride = (size_t)p.m * p.n;
-                float sum = 0.f;
-                for (uint32_t sl = 0; sl < contributors; sl += 8) {  // eight independent loads in flight, summed in order
-                    float v[8];
-#pragma unroll
-                    for (int i2 = 0; i2 < 8; ++i2) v[i2] = sl + i2 < contributors ? __ldcg(src + (sl + i2) * slice_stride) : 0.f;
-#pragma unroll
-                    for (int i2 = 0; i2 < 8; ++i2) sum += v[i2];
-                }
-                if (!GROUPED) sum *= load_scale(p.scale, nn, p.scale_dtype);
-                p.c[(size_t)mm * p.ldc + nn] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
-            }
-            if (tid == 0) p.counters[cb] = 0u;  // ready for the next launch
-        }
-    }
+    decode_finish<GROUPED>(p, s_red, s_last, cb, nblk, wk_count, MCOLS, cta_of);
     if (u < u_end) __syncthreads();   // the next piece reuses the ring (= the reduction buffer) and the flag word
     }   // pieces of work
 }
@@ -387,7 +283,7 @@ int resident_ctas(uint32_t bits, int mt, bool grouped) {
 
 bool decode_supports(const afb_gemm_args& a) {
     if (a.m == 0 || a.m > 16) return false;
-    if (a.b_layout != AFB_LAYOUT_COL) return false;
+    if (a.b_layout != AFB_LAYOUT_COL && a.b_layout != AFB_LAYOUT_COL_PACKED) return false;
     if (a.b_bits != 8 && a.b_bits != 4) return false;
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
     if (a.k % ch) return false;
@@ -402,7 +298,9 @@ bool decode_supports(const afb_gemm_args& a) {
 //   * wr: activations are re-read by every column of CTAs, so more activation rows ask for more channels per CTA
 //     (keeps the activation traffic through L2 below about half of the weight traffic);
 //   * slices: only when the channel dimension alone cannot fill the GPU.
-static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, DecodeParams& p) {
+// `stream`: the streaming form (decode_stream.cu): a pass of K need not be whole rounds of the WK warps there.
+static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, bool stream, size_t act_cap,
+                       DecodeParams& p) {
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
     const uint32_t sms = (uint32_t)sm_count;
     const uint32_t act_bytes_per_k = 2 * a.m;                      // per k, per column of CTAs
@@ -411,11 +309,10 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, si
     const double weight_mb = (double)a.n * a.k * a.b_bits / 8 / 1e6;
     auto ctas = [&](uint32_t w) { return (a.n + 16 * w - 1) / (16 * w); };
     while (wr < 8 && ctas(wr * 2) >= 6 * sms) wr *= 2;              // plenty of channels: larger CTAs, fewer activation re-reads
-    const size_t act_cap = (size_t)act_bytes(a.m <= 8 ? 1 : 2);
     // small matrices with 9 to 16 rows: when 16-channel CTAs alone fill the GPU, they beat wider CTAs with K-slices (no workspace
     // round trip; measured on 4096 x 4096: 10.2 vs 12.4 us at m = 9, 11.9 vs 12.6 at m = 12, equal at m = 16)
     if (weight_mb < 48.0 && a.m > 8 && ctas(1) >= sms * 3 / 2 && (size_t)a.m * (ch * kWarps * 2 + 16) <= act_cap) wr = 1;
-    while (wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > act_cap) wr *= 2;   // one round of the WK warps must fit the staging area
+    while (!stream && wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > act_cap) wr *= 2;   // one round of the WK warps must fit the staging area
     // the balanced form (below) pays off for more than 8 activation rows on large matrices (measured: 8 to 25 % there, a loss
     // of up to 10 % for m <= 8, whose grid form needs no K-slices); it runs best with the widest CTA
     bool want_balanced = weight_mb >= 48.0 && a.m > 8;
@@ -429,7 +326,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, si
     if (ctas(wr) > counter_count) s = 1;
     if (const char* e = getenv("AFB_DECODE_WR")) {       // tuning aid: force the CTA shape when it is legal
         const uint32_t v = (uint32_t)atoi(e);
-        if ((v == 1 || v == 2 || v == 4 || v == 8) && (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= act_cap) wr = v;
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && (stream || (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= act_cap)) wr = v;
     }
     if (const char* e = getenv("AFB_DECODE_SLICES")) {   // tuning aid: force the number of K-slices when it is legal
         const uint32_t v = (uint32_t)atoi(e);
@@ -437,7 +334,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, si
     }
     p.wr = wr; p.slices = s; p.kc = a.k / s;
     // activations staged per pass: as many k as fit the staging area, in whole rounds of the WK warps
-    const uint32_t round = ch * (kWarps / wr);
+    const uint32_t round = stream ? ch : ch * (kWarps / wr);
     uint32_t pass_max = ((uint32_t)act_cap / a.m - 16) / 2 / round * round;   // >= 512 k for m <= 16, round <= 512
     if (pass_max == 0) pass_max = round;
     const uint32_t npass = (p.kc + pass_max - 1) / pass_max;
@@ -488,7 +385,20 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
     p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
     const bool grouped = a.group_size != 0;
     const int mt = a.m <= 8 ? 1 : 2;
-    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, p);
+    const bool packed = a.b_layout == AFB_LAYOUT_COL_PACKED;
+    // two forms of the kernel: the streaming form is the default; AFB_DECODE_IMPL=staged selects the other (plain weights only)
+    static const bool env_staged = [] { const char* e = getenv("AFB_DECODE_IMPL"); return e && e[0] == 's' && e[1] == 't' && e[2] == 'a'; }();
+    const bool stream = packed || !env_staged;
+    if (stream) {
+        pick_shape(a, ctx->sm_count, decode_stream_resident(a.b_bits, mt, grouped), ws_bytes, counter_count, true, (size_t)decode_stream_act_bytes(mt), p);
+        p.ws = ws; p.counters = counters;
+        dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
+        if (p.streamk) grid = dim3(p.slices, 1);
+        const cudaError_t e = decode_stream_launch(a.b_bits, mt, grouped, packed, p, grid, (a.flags & AFB_FLAG_PDL) != 0, s);
+        count_launch();
+        return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+    }
+    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, false, (size_t)act_bytes(mt), p);
     p.ws = ws; p.counters = counters;
     dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
     if (p.streamk) grid = dim3(p.slices, 1);

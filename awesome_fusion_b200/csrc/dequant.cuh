@@ -93,6 +93,23 @@ __device__ __forceinline__ void s4x8_to_bf16_strided(uint32_t w, uint32_t magic,
     p[3] = s4pair_to_bf16x2(w >> 12, magic);
 }
 
+// Consecutive-k pairs {k0,k1},{k2,k3} of a word, whichever way the word is laid out: plain [k0,k1,k2,k3] needs two byte
+// permutes, the pre-packed order [k0,k2,k1,k3] (afb_prepack) is what the cheap routine reads as pairs.
+__device__ __forceinline__ void s8x4_to_bf16_pairs(uint32_t w, bool packed, uint32_t& p01, uint32_t& p23) {
+    if (packed) s8x4_to_bf16_strided(w, p01, p23);
+    else s8x4_to_bf16_natural(w, p01, p23);
+}
+__device__ __forceinline__ void s4x8_to_bf16_pairs(uint32_t w, uint32_t magic, bool packed, uint32_t p[4]) {
+    if (packed) s4x8_to_bf16_strided(w, magic, p);
+    else s4x8_to_bf16_natural(w, magic, p);
+}
+// Place of weight k inside its word in the pre-packed layout (int8: bytes [k0,k2,k1,k3]; int4: nibbles [k0,k2,k4,k6,k1,k3,k5,k7]).
+__host__ __device__ __forceinline__ uint32_t packed_pos(uint32_t bits, uint32_t k) {
+    if (bits == 8) { const uint32_t i = k & 3u; return (k & ~3u) | ((i >> 1) | ((i & 1u) << 1)); }
+    const uint32_t i = k & 7u;
+    return (k & ~7u) | ((i >> 1) | ((i & 1u) << 2));
+}
+
 __device__ __forceinline__ uint32_t bf16_dup(uint16_t s) { return (uint32_t)s * 0x00010001u; }
 
 }  // namespace afb

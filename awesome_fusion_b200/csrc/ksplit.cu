@@ -317,7 +317,7 @@ extern "C" int afb_ksplit_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, ui
 extern "C" int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_done, void* stream) {
     if (!args || !tile_done || !args->ptr_a || !args->ptr_b || !args->ptr_c || !args->ptr_scale) return AFB_ERR_BAD_ARG;
     if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;
-    if (args->lda < args->k || args->ldc < args->n || args->ldb < args->k || args->b_layout != AFB_LAYOUT_COL) return AFB_ERR_BAD_ARG;
+    if (args->lda < args->k || args->ldc < args->n || args->ldb < args->k || args->b_layout == AFB_LAYOUT_ROW || args->b_layout > 2) return AFB_ERR_BAD_ARG;
     if (!(args->flags & AFB_FLAG_C_F32)) return AFB_ERR_UNSUPPORTED;   // the partial sums travel as fp32
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;
@@ -335,7 +335,7 @@ extern "C" int afb_abi_sizes(uint32_t sizes[3]) {
 extern "C" int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream) {
     if (!args || !stage || !args->ptr_a || !args->ptr_b || !args->ptr_scale) return AFB_ERR_BAD_ARG;
     if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;
-    if (args->lda < args->k || args->ldb < args->k || args->b_layout != AFB_LAYOUT_COL) return AFB_ERR_BAD_ARG;
+    if (args->lda < args->k || args->ldb < args->k || args->b_layout == AFB_LAYOUT_ROW || args->b_layout > 2) return AFB_ERR_BAD_ARG;
     if (!(args->flags & AFB_FLAG_C_F32)) return AFB_ERR_UNSUPPORTED;   // the partial sums travel as fp32
     if (world == 0 || world > AFB_MAX_RANKS || rank >= world) return AFB_ERR_BAD_ARG;
     for (uint32_t q = 0; q < world; ++q) if (!stage[q] || (uintptr_t)stage[q] % 16) return AFB_ERR_BAD_ARG;

@@ -16,8 +16,9 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) { return __uint_as
 // Scalar decode of weight (n, k) -> integer value as float.
 __device__ __forceinline__ float load_q(const uint8_t* __restrict__ b, uint32_t n, uint32_t k, uint32_t ldb,
                                         uint32_t bits, uint32_t enc, uint32_t layout) {
+    if (layout == AFB_LAYOUT_COL_PACKED) k = packed_pos(bits, k);
     if (bits == 8) {
-        const size_t idx = layout == AFB_LAYOUT_COL ? (size_t)n * ldb + k : (size_t)k * ldb + n;
+        const size_t idx = layout != AFB_LAYOUT_ROW ? (size_t)n * ldb + k : (size_t)k * ldb + n;
         const uint8_t u = b[idx];
         const int v = enc == AFB_ENC_OFFSET_BINARY ? (int)u - 128 : (int)(int8_t)u;
         return (float)v;
@@ -73,7 +74,8 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
     const uint8_t* __restrict__ pb = reinterpret_cast<const uint8_t*>(a.ptr_b);
     const uint32_t xormask = a.b_encoding == AFB_ENC_OFFSET_BINARY ? 0x80808080u : 0u;
     const uint32_t magic4 = a.b_encoding == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
-    if (a.b_layout == AFB_LAYOUT_COL) {
+    const bool packed = a.b_layout == AFB_LAYOUT_COL_PACKED;
+    if (a.b_layout != AFB_LAYOUT_ROW) {
         const uint32_t per16 = a.b_bits == 8 ? 16u : 32u;  // weights per 16-byte piece
         const uint32_t pieces_per_row = a.k / per16;
         const size_t total = (size_t)a.n * pieces_per_row;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
                 sc = bf16_dup(sb);
             }
             uint32_t* o = reinterpret_cast<uint32_t*>(out + (size_t)n * a.k + k0);
-            if (a.flags & AFB_FLAG_DUMP_DECODE_PAIRING) {
+            if ((a.flags & AFB_FLAG_DUMP_DECODE_PAIRING) && !packed) {
                 // the decode kernel's unpack: cheap pairing ({k0,k2},{k1,k3} / {k0,k4}..{k3,k7}), integers only (that kernel
                 // applies group scales to fp32 partial sums, never to weights); stored back in natural k order
                 uint16_t* o16 = out + (size_t)n * a.k + k0;
@@ -118,7 +120,7 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t p01, p23;
-                    s8x4_to_bf16_natural(w[j] ^ xormask, p01, p23);
+                    s8x4_to_bf16_pairs(w[j] ^ xormask, packed, p01, p23);
                     if (a.group_size) { p01 = bf16x2_mul(p01, sc); p23 = bf16x2_mul(p23, sc); }
                     o[2 * j] = p01; o[2 * j + 1] = p23;
                 }
@@ -126,7 +128,7 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t p[4];
-                    s4x8_to_bf16_natural(w[j], magic4, p);
+                    s4x8_to_bf16_pairs(w[j], magic4, packed, p);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) o[4 * j + i] = a.group_size ? bf16x2_mul(p[i], sc) : p[i];
                 }
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
 }
 
 int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s) {
-    if (a.b_layout == AFB_LAYOUT_COL) {
+    if (a.b_layout != AFB_LAYOUT_ROW) {
         const uint32_t per16 = a.b_bits == 8 ? 16u : 32u;
         if (a.k % per16 || (a.b_bits == 8 ? a.ldb % 16 : a.ldb % 32)) return AFB_ERR_UNSUPPORTED;
         if (a.group_size && a.group_size % 32) return AFB_ERR_UNSUPPORTED;

@@ -57,7 +57,7 @@ extern "C" int afb_gemm_launch_static(const afb_gemm_args* args, void* stream) {
     if (args->lda < args->k || args->ldc < args->n || args->ldb < args->k) return AFB_ERR_BAD_ARG;
     if (args->variant != AFB_VARIANT_AUTO && args->variant != AFB_VARIANT_DECODE) return AFB_ERR_UNSUPPORTED;
     if (args->b_bits != 8 && args->b_bits != 4) return AFB_ERR_BAD_ARG;
-    if (args->b_encoding > 1 || args->b_layout > 1 || args->scale_dtype > 1) return AFB_ERR_BAD_ARG;
+    if (args->b_encoding > 1 || args->b_layout > 2 || args->scale_dtype > 1) return AFB_ERR_BAD_ARG;
     if ((uintptr_t)args->ptr_scale % (args->scale_dtype == AFB_SCALE_BF16 ? 2 : 4) || (uintptr_t)args->ptr_c % 2) return AFB_ERR_BAD_ARG;
     if (!decode_supports(*args)) return AFB_ERR_UNSUPPORTED;           // M <= 16, [N,K] layout, see afb_capi.h
     if ((size_t)args->m * args->n > kMaxOutputs) return AFB_ERR_TOO_LARGE;

@@ -37,6 +37,7 @@ struct PrefillParams {
     uint32_t enc, scale_dtype, group;
     uint32_t m_tiles, n_tiles;
     uint32_t c_f32;     // 1: C is fp32 (partial sums of a K-split), 0: bf16
+    uint32_t packed;    // B is in the pre-packed order of afb_prepack
     int32_t* status;
 };
 
@@ -293,7 +294,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         uint32_t o[8];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            s8x4_to_bf16_natural(w[j] ^ xormask, o[2 * j], o[2 * j + 1]);
+                            s8x4_to_bf16_pairs(w[j] ^ xormask, p.packed != 0, o[2 * j], o[2 * j + 1]);
                             if (GROUPED) { o[2 * j] = bf16x2_mul(o[2 * j], sc_cur[itx]); o[2 * j + 1] = bf16x2_mul(o[2 * j + 1], sc_cur[itx]); }
                         }
                         *reinterpret_cast<uint4*>(orow + (((2 * piece) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -302,7 +303,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             uint32_t q[4];
-                            s4x8_to_bf16_natural(w[j], magic4, q);
+                            s4x8_to_bf16_pairs(w[j], magic4, p.packed != 0, q);
                             if (GROUPED) {
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) q[e] = bf16x2_mul(q[e], sc_cur[itx]);
@@ -362,6 +363,7 @@ int launch_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
     p.m_tiles = (a.m + BM - 1) / BM;
     p.n_tiles = (a.n + BN - 1) / BN;
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
+    p.packed = a.b_layout == AFB_LAYOUT_COL_PACKED ? 1u : 0u;
     p.status = ctx->status;
     auto kern = prefill_kernel<BITS, GROUPED, BN>;
     static DeviceOnce attr_set;  // per template instance
@@ -381,7 +383,7 @@ int launch_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
 }  // namespace
 
 bool prefill_supports(const afb_gemm_args& a) {
-    if (a.b_layout != AFB_LAYOUT_COL) return false;
+    if (a.b_layout != AFB_LAYOUT_COL && a.b_layout != AFB_LAYOUT_COL_PACKED) return false;
     if (a.b_bits != 8 && a.b_bits != 4) return false;
     if (a.m == 0 || a.n == 0 || a.k == 0) return false;
     if (a.k % BK || a.n % 8) return false;

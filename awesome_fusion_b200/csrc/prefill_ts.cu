@@ -45,6 +45,7 @@ struct TsParams {
     uint32_t m_rot;        // row tiles are taken in rotated order, starting at this one (spreads the peers a rank pushes to)
     uint32_t group_m;      // tile order: groups of group_m row tiles; inside a group the channel tiles advance, row tile fastest
     uint32_t c_f32;
+    uint32_t packed;       // B is in the pre-packed order of afb_prepack: the cheap unpack yields consecutive k
     uint32_t exact;        // group scales only: the weight q * s goes to the tensor cores as TWO bf16 terms, hi = bf16_rn(q * s) and
                            // lo = q * s - hi (exact: the product has at most 16 significant bits), in two TMEM slots and two MMAs
     uint32_t* tile_done;   // optional: per-tile counters, +kWorkerWarps when a tile of C has been stored (system-scope release)
@@ -247,6 +248,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         const uint32_t ch = q * 32 + lane;                    // channel (TMEM lane) of this thread inside the tile
         const uint32_t xormask = (BITS == 8 && p.enc == AFB_ENC_OFFSET_BINARY) ? 0x80808080u : 0u;
         const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
+        const bool packed = p.packed != 0;
         const uint32_t groups_per_row = GROUPED ? p.k / p.group : 0;
         const uint32_t kb_per_group = GROUPED ? p.group / BK : 1;
         // raw tile in shared memory: rows of 64 (int8) / 32 (int4) bytes, stored by TMA with the 64- / 32-byte swizzle
@@ -302,10 +304,10 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
 #pragma unroll
                 for (int j = 0; j < kWords; ++j) {
                     if (BITS == 8) {
-                        s8x4_to_bf16_natural(w[j] ^ xormask, o[2 * j], o[2 * j + 1]);
+                        s8x4_to_bf16_pairs(w[j] ^ xormask, packed, o[2 * j], o[2 * j + 1]);
                     } else {
                         uint32_t qv[4];
-                        s4x8_to_bf16_natural(w[j], magic4, qv);
+                        s4x8_to_bf16_pairs(w[j], magic4, packed, qv);
                         o[4 * j] = qv[0]; o[4 * j + 1] = qv[1]; o[4 * j + 2] = qv[2]; o[4 * j + 3] = qv[3];
                     }
                 }
@@ -563,6 +565,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.n_tiles = (a.n + BNW - 1) / BNW;
     p.c_f32 = (a.flags & AFB_FLAG_C_F32) ? 1u : 0u;
     p.exact = (GROUPED && (a.flags & AFB_FLAG_GROUP_EXACT)) ? 1u : 0u;
+    p.packed = a.b_layout == AFB_LAYOUT_COL_PACKED ? 1u : 0u;
     p.group_m = tile_done ? p.m_tiles : pick_group_m(a, p.m_tiles, p.n_tiles, BMA, ctx->sm_count);   // the exchange kernel assumes row-tile-fastest order
     p.tile_done = tile_done;
     // The tiles beyond the last full wave would keep a few SMs busy for a whole tile while the rest idle: cut each of them into

@@ -38,6 +38,7 @@ extern "C" {
 
 #define AFB_LAYOUT_ROW 0u /* B is [K,N], N contiguous — the reference's "rrr" (bfAintBGemm.cc:20-23,51) */
 #define AFB_LAYOUT_COL 1u /* B is [N,K], K contiguous — ColumnMajor tag of gemm_tensor_layout.hpp:16-19 */
+#define AFB_LAYOUT_COL_PACKED 2u /* [N,K] as written by afb_prepack: same rows and pitch, weights reordered inside every 32-bit word */
 
 #define AFB_SCALE_F32  0u
 #define AFB_SCALE_BF16 1u
@@ -57,6 +58,10 @@ extern "C" {
                                    (hi = bf16_rn(q * s), lo = q * s - hi, exact) instead of the one rounded term: twice the tensor-core
                                    work, and the result is that of the fp32 formula of host_ref.hpp:15-24 up to summation order.
                                    No effect where the scale never touches the weights (per-channel scales, decode variant). */
+#define AFB_FLAG_PDL 64u /* decode variant: launch with programmatic stream serialisation.  The kernel starts streaming B while the preceding
+                           kernel of the stream is still running and waits for it only before it touches A, C or the workspace; it
+                           also lets its own successor start early.  The caller promises that B and the scales are NOT written by
+                           the kernel that precedes this launch on the stream (weights are constants in a decode loop). */
 #define AFB_FLAG_DUMP_DECODE_PAIRING 16u /* afb_dequant_dump only ([N,K] layout): unpack with the decode kernel's routines (strided pairing,
                                          integer values, no scale) instead of the prefill kernel's; the output is in natural k order either way */
 
@@ -142,6 +147,16 @@ int afb_gemm_host(const afb_gemm_args* host_args, void* stream);
  * takes the rest of the memory and before any stream capture (or run with CUDA_MODULE_LOADING=EAGER).  From
  * the second call on, nothing is allocated by anyone. */
 int afb_gemm_launch_static(const afb_gemm_args* args, void* stream);
+/* Weight pre-packing, the offline step before the GEMM (extends the reference's host-side format conversion,
+ * mem_transfer.hpp:12-32 called at bfAintBGemm.cc:96-97).  Reads args->ptr_b / n / k / ldb / b_bits / b_layout
+ * (AFB_LAYOUT_ROW [K,N] int8, or AFB_LAYOUT_COL [N,K] int8 / int4) and writes the same integers as
+ * AFB_LAYOUT_COL_PACKED into out_b: [N,K], pitch out_ldb elements, inside every 32-bit word the order
+ *   int8: bytes [k0,k2,k1,k3]      int4: nibbles [k0,k2,k4,k6,k1,k3,k5,k7]
+ * which is the order the kernels' unpack reads as pairs, so they skip the re-pairing of the activations (decode)
+ * or of the weights (prefill).  A GEMM on the result sets b_layout = AFB_LAYOUT_COL_PACKED, ptr_b = out_b,
+ * ldb = out_ldb; its result is bit-identical to the GEMM on the plain [N,K] weights.  [N,K] input may be packed
+ * in place (out_b == ptr_b, out_ldb == ldb).  Asynchronous on `stream`. */
+int afb_prepack(const afb_gemm_args* args, void* out_b, uint32_t out_ldb, void* stream);
 /* Dequantised weights exactly as the kernels feed them to the tensor cores:
  * out is bf16 with B's logical shape and layout ([N,K] ld=K for COL, [K,N] ld=N for ROW).
  * group_size == 0: the exact integer value; else bf16_rn(float(q) * float(scale)).

@@ -54,15 +54,25 @@ struct Args {
     uint32_t bits, enc, layout, scale_dtype, group;
 };
 
-// Integer value of weight (n, k), exact.
+// Position of weight k inside its 32-bit word in the pre-packed [N,K] layout (layout 2): the GPU kernels' cheap unpack
+// takes bytes (0,2),(1,3) / nibbles (0,4),(1,5),(2,6),(3,7) of a word as pairs, so consecutive k sit at those places:
+//   int8: word bytes   = [k0,k2,k1,k3]           int4: word nibbles = [k0,k2,k4,k6,k1,k3,k5,k7]
+inline uint32_t packed_pos(uint32_t bits, uint32_t k) {
+    if (bits == 8) { const uint32_t i = k & 3u; return (k & ~3u) | ((i >> 1) | ((i & 1u) << 1)); }
+    const uint32_t i = k & 7u;
+    return (k & ~7u) | ((i >> 1) | ((i & 1u) << 2));
+}
+
+// Integer value of weight (n, k), exact.  layout 0: [K,N]; 1: [N,K]; 2: [N,K] pre-packed.
 inline int weight_q(const uint8_t* b, const Args& a, uint32_t n, uint32_t k) {
+    const uint32_t kk = a.layout == 2 ? packed_pos(a.bits, k) : k;
     if (a.bits == 8) {
-        const size_t idx = a.layout == 1 ? (size_t)n * a.ldb + k : (size_t)k * a.ldb + n;
+        const size_t idx = a.layout != 0 ? (size_t)n * a.ldb + kk : (size_t)k * a.ldb + n;
         const uint8_t u = b[idx];
         return a.enc == 1 ? (int)u - 128 : (int)(int8_t)u;
     }
-    const uint8_t byte = b[(size_t)n * (a.ldb / 2) + k / 2];
-    const int nib = (k & 1) ? (byte >> 4) : (byte & 0xF);
+    const uint8_t byte = b[(size_t)n * (a.ldb / 2) + kk / 2];
+    const int nib = (kk & 1) ? (byte >> 4) : (byte & 0xF);
     return a.enc == 1 ? nib - 8 : (nib >= 8 ? nib - 16 : nib);
 }
 inline float scale_at(const void* s, const Args& a, uint32_t n, uint32_t k) {
@@ -125,8 +135,25 @@ void afb_oracle_dequant_bf16(uint16_t* out, const uint8_t* b, const void* scale,
         for (uint32_t ik = 0; ik < k; ++ik) {
             float w = (float)weight_q(b, a, in, ik);
             if (group) w = w * scale_at(scale, a, in, ik);
-            const size_t o = layout == 1 ? (size_t)in * k + ik : (size_t)ik * n + in;
+            const size_t o = layout != 0 ? (size_t)in * k + ik : (size_t)ik * n + in;
             out[o] = f32_to_bf16_rne(w);
+        }
+}
+
+// Weight pre-packing, restated: B in layout 0 ([K,N], int8) or 1 ([N,K]) -> layout 2 ([N,K], pitch out_ldb elements), the
+// stored integers unchanged, only moved (the host-side format step this extends is mem_transfer.hpp:12-32).
+void afb_oracle_prepack(uint8_t* out, const uint8_t* b, uint32_t n, uint32_t k, uint32_t ldb, uint32_t out_ldb, uint32_t bits, uint32_t layout) {
+    for (uint32_t in = 0; in < n; ++in)
+        for (uint32_t ik = 0; ik < k; ++ik) {
+            const uint32_t kk = packed_pos(bits, ik);
+            if (bits == 8) {
+                out[(size_t)in * out_ldb + kk] = layout == 0 ? b[(size_t)ik * ldb + in] : b[(size_t)in * ldb + ik];
+            } else {
+                const uint8_t src = b[(size_t)in * (ldb / 2) + ik / 2];
+                const uint8_t nib = (ik & 1) ? (src >> 4) : (src & 0xF);
+                uint8_t& dst = out[(size_t)in * (out_ldb / 2) + kk / 2];
+                dst = (kk & 1) ? (uint8_t)((dst & 0x0F) | (nib << 4)) : (uint8_t)((dst & 0xF0) | nib);
+            }
         }
 }
 

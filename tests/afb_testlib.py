@@ -30,6 +30,7 @@ class Oracle:
         L.afb_oracle_f32_to_i4.argtypes = [_f32p, _u8p, sz, u32]
         L.afb_oracle_dequant_bf16.argtypes = [_u16p, _u8p, vp, u32, u32, u32, u32, u32, u32, u32, u32]
         L.afb_oracle_gemm.argtypes = [_f32p, _u16p, _u8p, vp] + [u32] * 11 + [i, i]
+        L.afb_oracle_prepack.argtypes = [_u8p, _u8p] + [u32] * 6
         L.afb_oracle_gemm_rrr.argtypes = [_f32p, _f32p, _f32p, _f32p] + [sz] * 6
         L.afb_oracle_compare.argtypes = [_f32p, _u16p, sz, ctypes.c_float, ctypes.POINTER(ctypes.c_double),
                                          ctypes.POINTER(ctypes.c_double), ctypes.POINTER(sz)]
@@ -67,11 +68,19 @@ class Oracle:
 
     def dequant_bf16(self, case):
         c = case
-        shape = (c.n, c.k) if c.layout == 1 else (c.k, c.n)
+        shape = (c.n, c.k) if c.layout != 0 else (c.k, c.n)
         out = np.empty(shape, np.uint16)
         self.lib.afb_oracle_dequant_bf16(_p(out, _u16p), _p(c.b, _u8p), c.scale.ctypes.data, c.n, c.k, c.ldb, c.bits, c.enc,
                                          c.layout, c.scale_dtype, c.group)
         return out
+
+    def prepack(self, case, out_ldb=None):
+        """The Case with B pre-packed (layout 2), by the CPU restatement of afb_prepack."""
+        c = case
+        out_ldb = out_ldb or c.k
+        out = np.zeros((c.n, out_ldb * c.bits // 8), np.uint8)
+        self.lib.afb_oracle_prepack(_p(out, _u8p), _p(c.b, _u8p), c.n, c.k, c.ldb, out_ldb, c.bits, c.layout)
+        return Case(**{**c.__dict__, "b": out, "layout": 2, "ldb": out_ldb})
 
     def gemm(self, case, round_w=False, threads=1, rows=None):
         """fp32 C of the oracle; ``rows`` restricts to a list of activation rows (used at full sizes)."""

@@ -194,6 +194,21 @@ def main():
     assert mx <= 1e-2, f"nccl path: {mx}"
     for p in (d_a, d_b, d_s):
         lib.free(p)
+    # the benchmark's own step object with its default exchange for this world size (at 8 ranks: forwarding warps, rotated
+    # push order, multicast broadcast), on a reduced shape, checked by the benchmark's own parity routine
+    import bench
+    mlp = D.ShardedMLP(lib, torch, rank=rank, world=world, exchange="auto", m=256 * world, up=(256 * world, 1024), down=(1024, 512 * world), seed=5)
+    for _ in range(3):
+        mlp.step(stream)
+    torch.cuda.synchronize()
+    par = bench.parity_check(mlp, torch, world, rank)
+    st = lib.read_status()
+    assert st[0] == 0, f"device status {st}"
+    assert par["ok"], par
+    if rank == 0:
+        print(f"sharded step ({mlp.exchange_name}): max rel err {par['max_rel']:.3e} nrms {par['nrms']:.3e}", flush=True)
+    tdist.barrier(); torch.cuda.synchronize()
+    mlp.close()
     tdist.barrier()
     if rank == 0:
         print("DIST-OK gpu")
