@@ -20,6 +20,7 @@ FLAG_PUSH_VIA_LOCAL = 8
 FLAG_DUMP_DECODE_PAIRING = 16
 FLAG_GROUP_EXACT = 32
 FLAG_PDL = 64
+ACT_NONE, ACT_SILU = 0, 1
 IPC_HANDLE_BYTES = 64
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -30,7 +31,7 @@ EXPORTS = [
     "afb_free_host", "afb_memcpy_h2d", "afb_memcpy_d2h", "afb_memcpy_d2d", "afb_memset", "afb_event_create",
     "afb_event_record", "afb_event_sync", "afb_event_elapsed_ms", "afb_event_destroy", "afb_stream_create",
     "afb_stream_sync", "afb_stream_destroy", "afb_device_sync", "afb_gemm_launch", "afb_gemm_resolve_variant",
-    "afb_gemm_host", "afb_gemm_launch_static", "afb_prepack", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
+    "afb_gemm_host", "afb_gemm_launch_static", "afb_prepack", "afb_prepack_gated", "afb_gemm_fused_launch", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
     "afb_ksplit_allreduce_launch", "afb_cast_f32_to_bf16", "afb_ksplit_tile_info", "afb_gemm_launch_tiles", "afb_ksplit_tile_allreduce_launch", "afb_gemm_launch_push", "afb_abi_sizes",
     "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
 ]
@@ -51,7 +52,14 @@ class GemmArgs(ctypes.Structure):
         ("b_bits", ctypes.c_uint32), ("b_encoding", ctypes.c_uint32), ("b_layout", ctypes.c_uint32),
         ("scale_dtype", ctypes.c_uint32), ("group_size", ctypes.c_uint32), ("variant", ctypes.c_uint32),
         ("flags", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
+        ("ptr_zero", ctypes.c_void_p), ("reserved2", ctypes.c_uint64),
     ]
+
+
+class FusedArgs(ctypes.Structure):
+    """``afb_fused_args``: a GEMM plus its fused epilogue (bias, activation, gate * up, residual)."""
+    _fields_ = [("gemm", GemmArgs), ("gated", ctypes.c_uint32), ("activation", ctypes.c_uint32), ("ptr_bias", ctypes.c_void_p),
+                ("ptr_residual", ctypes.c_void_p), ("ld_residual", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
 def library_path() -> str:
@@ -105,6 +113,8 @@ class Library:
         L.afb_gemm_launch_static.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_dequant_dump.argtypes = [ctypes.POINTER(GemmArgs), vp, vp]
         L.afb_prepack.argtypes = [ctypes.POINTER(GemmArgs), vp, ctypes.c_uint32, vp]
+        L.afb_prepack_gated.argtypes = [ctypes.POINTER(GemmArgs), vp, vp, vp, vp, ctypes.c_uint32, vp, vp, vp]
+        L.afb_gemm_fused_launch.argtypes = [ctypes.POINTER(FusedArgs), vp]
         L.afb_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
         L.afb_ipc_export.argtypes = [vp, ctypes.c_char_p]
         L.afb_ipc_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
@@ -223,7 +233,7 @@ class Library:
     # ---- the hot path ------------------------------------------------------------
     @staticmethod
     def make_args(c, a, b, scale, m, n, k, *, lda=None, ldb=None, ldc=None, bits=8, encoding=ENC_TWOS,
-                  layout=LAYOUT_COL, scale_dtype=SCALE_F32, group=0, variant=VARIANT_AUTO, flags=0):
+                  layout=LAYOUT_COL, scale_dtype=SCALE_F32, group=0, variant=VARIANT_AUTO, flags=0, zero=None):
         args = GemmArgs()
         args.ptr_c, args.ptr_a, args.ptr_b, args.ptr_scale = _ptr(c), _ptr(a), _ptr(b), _ptr(scale)
         args.m, args.n, args.k = m, n, k
@@ -232,6 +242,7 @@ class Library:
         args.ldc = n if ldc is None else ldc
         args.b_bits, args.b_encoding, args.b_layout = bits, encoding, layout
         args.scale_dtype, args.group_size, args.variant, args.flags, args.reserved = scale_dtype, group, variant, flags, 0
+        args.ptr_zero, args.reserved2 = _ptr(zero), 0
         return args
 
     def gemm_launch_status(self, args, stream=None):
@@ -255,6 +266,25 @@ class Library:
     def prepack(self, args, out_b, out_ldb, stream=None):
         """afb_prepack: B of `args` ([K,N] or [N,K]) -> the pre-packed [N,K] layout in `out_b`."""
         self.check(self.lib.afb_prepack(ctypes.byref(args), _ptr(out_b), out_ldb, stream), "afb_prepack")
+
+    def prepack_gated(self, gate_args, b_up, scale_up, zero_up, out_b, out_ldb, out_scale, out_zero=None, stream=None):
+        """afb_prepack_gated: gate / up projections -> one row-interleaved, pre-packed B with interleaved scales (and zero-points)."""
+        self.check(self.lib.afb_prepack_gated(ctypes.byref(gate_args), _ptr(b_up), _ptr(scale_up), _ptr(zero_up), _ptr(out_b), out_ldb,
+                                              _ptr(out_scale), _ptr(out_zero), stream), "afb_prepack_gated")
+
+    @staticmethod
+    def make_fused_args(gemm_args, *, gated=False, activation=ACT_NONE, bias=None, residual=None, ld_residual=0):
+        f = FusedArgs()
+        f.gemm = gemm_args
+        f.gated, f.activation = int(gated), activation
+        f.ptr_bias, f.ptr_residual, f.ld_residual, f.reserved = _ptr(bias), _ptr(residual), ld_residual, 0
+        return f
+
+    def gemm_fused_launch_status(self, fused_args, stream=None):
+        return self.lib.afb_gemm_fused_launch(ctypes.byref(fused_args), stream)
+
+    def gemm_fused_launch(self, fused_args, stream=None):
+        self.check(self.lib.afb_gemm_fused_launch(ctypes.byref(fused_args), stream), "afb_gemm_fused_launch")
 
     def dequant_dump(self, args, out, stream=None):
         self.check(self.lib.afb_dequant_dump(ctypes.byref(args), _ptr(out), stream), "afb_dequant_dump")

@@ -62,7 +62,7 @@ int launch_decode(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);
 int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t ws_bytes, uint32_t* counters,
                      size_t counter_count, cudaStream_t s);
 int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);      // converted weights through shared memory
-int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);   // converted weights in tensor memory
+int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, const afb_fused_args* fused = nullptr);   // converted weights in tensor memory
 int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* tile_done, cudaStream_t s);
 int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s);
 void prefill_ts_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* m_tiles, uint32_t* n_tiles, uint32_t* arrivals);
@@ -70,5 +70,6 @@ int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s);
 
 bool decode_supports(const afb_gemm_args& a);
 bool prefill_supports(const afb_gemm_args& a);
+bool prefill_needs_ts(const afb_gemm_args& a);   // groups of 32 or zero-points: only the tensor-memory form
 
 }  // namespace afb

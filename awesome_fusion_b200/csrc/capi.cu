@@ -17,6 +17,7 @@ std::atomic<int> g_last_cuda_error{0};
 std::atomic<unsigned long long> g_launches{0};
 constexpr size_t kSplitKWorkspaceBytes = 32u << 20;
 constexpr size_t kSplitKCounters = 4096;
+constexpr int kPreallocatedWorkspaces = 4;
 constexpr uint32_t kPrefillTsMinM = 128;   // measured: above 128 activation rows the tensor-memory form is 1.3x faster, at 128 it is slower
 }  // namespace
 
@@ -38,7 +39,7 @@ const DeviceCtx::Workspace* workspace_for(DeviceCtx* ctx, cudaStream_t s, int* r
     DeviceCtx::Workspace* free_slot = nullptr;
     for (auto& w : ctx->workspaces) {
         if (w.assigned && w.stream == s) return &w;
-        if (!w.assigned && !free_slot) free_slot = &w;
+        if (!w.assigned && (!free_slot || (w.ws && !free_slot->ws))) free_slot = &w;   // an unassigned slot that already has memory first
     }
     if (!free_slot) { *rc = AFB_ERR_TOO_LARGE; return nullptr; }   // more streams than workspaces
     if (!free_slot->ws) {
@@ -71,16 +72,18 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-static int validate(const afb_gemm_args* a) {
+// n_out: columns of C (differs from a->n, the rows of B, only for the gated fused launch)
+static int validate(const afb_gemm_args* a, uint32_t n_out = 0) {
     if (!a) return AFB_ERR_BAD_ARG;
+    if (n_out == 0) n_out = a->n;
     if (!a->ptr_a || !a->ptr_b || !a->ptr_c || !a->ptr_scale) return AFB_ERR_BAD_ARG;
     if (a->m == 0 || a->n == 0 || a->k == 0) return AFB_ERR_BAD_ARG;
-    if (a->reserved != 0) return AFB_ERR_BAD_ARG;
+    if (a->reserved != 0 || a->reserved2 != 0) return AFB_ERR_BAD_ARG;
     if (a->b_bits != 8 && a->b_bits != 4) return AFB_ERR_BAD_ARG;
     if (a->b_encoding > 1 || a->b_layout > 2 || a->scale_dtype > 1 || a->variant > 3) return AFB_ERR_BAD_ARG;
-    if (a->flags & ~(AFB_FLAG_C_F32 | AFB_FLAG_PREFILL_SMEM_B | AFB_FLAG_PREFILL_TMEM_A | AFB_FLAG_GROUP_EXACT)) return AFB_ERR_BAD_ARG;
+    if (a->flags & ~(AFB_FLAG_C_F32 | AFB_FLAG_PREFILL_SMEM_B | AFB_FLAG_PREFILL_TMEM_A | AFB_FLAG_GROUP_EXACT | AFB_FLAG_PDL)) return AFB_ERR_BAD_ARG;
     if ((a->flags & AFB_FLAG_GROUP_EXACT) && (a->flags & AFB_FLAG_PREFILL_SMEM_B) && a->group_size) return AFB_ERR_UNSUPPORTED;   // only the tensor-memory form has it
-    if (a->lda < a->k || a->ldc < a->n) return AFB_ERR_BAD_ARG;
+    if (a->lda < a->k || a->ldc < n_out) return AFB_ERR_BAD_ARG;
     if (a->b_layout != AFB_LAYOUT_ROW ? a->ldb < a->k : a->ldb < a->n) return AFB_ERR_BAD_ARG;
     if (a->b_bits == 4 && (a->b_layout == AFB_LAYOUT_ROW || (a->k & 1) || (a->ldb & 1))) return AFB_ERR_UNSUPPORTED;
     if (a->b_layout == AFB_LAYOUT_COL_PACKED && a->k % (a->b_bits == 8 ? 4u : 8u)) return AFB_ERR_BAD_ARG;   // whole words
@@ -137,9 +140,13 @@ int afb_init(int device) {
     AFB_CUDA(cudaMemset(c.status, 0, 4 * sizeof(int32_t)));
     c.splitk_ws_bytes = kSplitKWorkspaceBytes;
     c.splitk_counter_count = kSplitKCounters;
-    AFB_CUDA(cudaMalloc(&c.workspaces[0].ws, kSplitKWorkspaceBytes));
-    AFB_CUDA(cudaMalloc(&c.workspaces[0].counters, kSplitKCounters * sizeof(uint32_t)));
-    AFB_CUDA(cudaMemset(c.workspaces[0].counters, 0, kSplitKCounters * sizeof(uint32_t)));
+    // the first few workspaces exist from the start, so that a stream's first launch may also happen inside a stream capture
+    // (frameworks capture on a fresh stream); further streams allocate theirs on first use, outside capture
+    for (int i = 0; i < kPreallocatedWorkspaces; ++i) {
+        AFB_CUDA(cudaMalloc(&c.workspaces[i].ws, kSplitKWorkspaceBytes));
+        AFB_CUDA(cudaMalloc(&c.workspaces[i].counters, kSplitKCounters * sizeof(uint32_t)));
+        AFB_CUDA(cudaMemset(c.workspaces[i].counters, 0, kSplitKCounters * sizeof(uint32_t)));
+    }
     AFB_CUDA(cudaMalloc(&c.ar_words, 4 * sizeof(uint32_t)));
     AFB_CUDA(cudaMemset(c.ar_words, 0, 4 * sizeof(uint32_t)));
     AFB_CUDA(cudaDeviceSynchronize());
@@ -258,10 +265,31 @@ int afb_gemm_launch(const afb_gemm_args* args, void* stream) {
             if (args->flags & AFB_FLAG_PREFILL_SMEM_B) ts = false;
             if (args->flags & AFB_FLAG_PREFILL_TMEM_A) ts = true;
             if ((args->flags & AFB_FLAG_GROUP_EXACT) && args->group_size) ts = true;
+            if (prefill_needs_ts(*args)) {
+                if (args->flags & AFB_FLAG_PREFILL_SMEM_B) return AFB_ERR_UNSUPPORTED;
+                ts = true;
+            }
             return ts ? launch_prefill_ts(*args, ctx, s) : launch_prefill(*args, ctx, s);
         }
         default:                  return launch_naive(*args, ctx, s);
     }
+}
+
+int afb_gemm_fused_launch(const afb_fused_args* f, void* stream) {
+    if (!f || f->reserved != 0 || f->gated > 1 || f->activation > AFB_ACT_SILU) return AFB_ERR_BAD_ARG;
+    const afb_gemm_args& a = f->gemm;
+    if (f->gated && (a.n & 1u)) return AFB_ERR_BAD_ARG;
+    const uint32_t n_out = f->gated ? a.n / 2 : a.n;
+    int rc = validate(&a, n_out);
+    if (rc) return rc;
+    if (a.flags & ~(AFB_FLAG_GROUP_EXACT | AFB_FLAG_PREFILL_TMEM_A)) return AFB_ERR_UNSUPPORTED;   // bf16 output, tensor-memory form
+    if (a.variant != AFB_VARIANT_AUTO && a.variant != AFB_VARIANT_PREFILL) return AFB_ERR_UNSUPPORTED;
+    if ((uintptr_t)f->ptr_bias % 4 || (uintptr_t)f->ptr_residual % 2) return AFB_ERR_BAD_ARG;
+    if (f->ptr_residual && f->ld_residual < n_out) return AFB_ERR_BAD_ARG;
+    if (!prefill_supports(a)) return AFB_ERR_UNSUPPORTED;   // [N,K] layout (plain or pre-packed), K % 64 == 0, aligned pointers and pitches
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    return launch_prefill_ts(a, ctx, (cudaStream_t)stream, f);
 }
 
 static size_t b_bytes(const afb_gemm_args& a) {

@@ -29,30 +29,36 @@ namespace afb {
 
 namespace {
 
-#ifndef AFB_DECODE_RING
-#define AFB_DECODE_RING 4
-#endif
 #ifndef AFB_DECODE_MT1_CTAS
 #define AFB_DECODE_MT1_CTAS 4
 #endif
 #ifndef AFB_DECODE_MT2_CTAS
 #define AFB_DECODE_MT2_CTAS 3
 #endif
-constexpr int kRing = AFB_DECODE_RING;         // cp.async stages per warp (power of two)
-constexpr int kRingBytes = kWarps * kRing * kStageBytes;   // 32 KiB
+// cp.async stages per warp (RING, a power of two): 4 for large matrices (32 KiB per CTA, up to four CTAs per SM), 8 for matrices so
+// small that a warp owns at most 8 chunks (64 KiB per CTA, two CTAs per SM): its whole share of the weights is then in flight
+// before the kernel has to wait for anything else, which is what a launch with AFB_FLAG_PDL overlaps with its predecessor.
+__host__ __device__ constexpr int ring_bytes(int ring) { return kWarps * ring * kStageBytes; }
 // staged activations of one pass, m rows x (pass_k * 2 + 16) bytes: 20 KiB for m <= 8 (52 KiB per CTA: four CTAs per SM, 64 registers),
 // 40 KiB for m <= 16 (72 KiB per CTA: three CTAs per SM, 80 registers)
 __host__ __device__ constexpr int act_bytes(int mt) { return mt == 1 ? 20 * 1024 : 40 * 1024; }
 constexpr int kOffRed = 0;
-constexpr int kOffAct = kRingBytes;
-__host__ __device__ constexpr int smem_bytes(int mt) { return kOffAct + act_bytes(mt) + 16; }
-static_assert(kRedFloats * 4 <= kRingBytes, "the reduction buffer must fit the ring it reuses");
+__host__ __device__ constexpr int smem_bytes(int mt, int ring) { return ring_bytes(ring) + act_bytes(mt) + 16; }
+static_assert(kRedFloats * 4 <= ring_bytes(4), "the reduction buffer must fit the ring it reuses");
 
-template <int BITS, int MT, bool GROUPED>
+__device__ __forceinline__ void grid_dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ZP (int8 only): zero-points cost one more packed subtraction per pair of weights; int4 zero-points ride on the constant the
+// unpack subtracts anyway, so those instances take them without a switch.
+template <int BITS, int MT, bool GROUPED, bool ZP, int RING>
 // resident CTAs per SM the register budget is cut for: the group-scaled int4 kernels want more registers than the others (16 rows:
 // about 118, 12 % faster with two CTAs and no spills than with three squeezed into 80; 8 rows: 80, 3 to 8 % faster with three
 // CTAs than with four at 64); the other kernels gain nothing or lose (measured)
-__global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 3 : 2) : (MT == 1 ? AFB_DECODE_MT1_CTAS : AFB_DECODE_MT2_CTAS)) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, RING == 8 ? 2 : ((BITS == 4 && GROUPED) ? (MT == 1 ? 3 : 2) : (MT == 1 ? AFB_DECODE_MT1_CTAS : AFB_DECODE_MT2_CTAS)))
+decode_kernel(const DecodeParams p) {
+    constexpr int kRing = RING;
+    constexpr int kOffAct = ring_bytes(RING);
     constexpr int CH = BITS == 8 ? 64 : 128;    // k per chunk (a quad covers 64 bytes of one channel)
     constexpr int LK = CH / 4;                  // k per lane per chunk
     constexpr int AV = LK / 8;                  // 16-byte activation vectors per lane, row and chunk
@@ -70,6 +76,12 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
     const uint32_t groups_per_row = GROUPED ? (p.k >> p.group_shift) : 0;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * (kRing * kStageBytes) + lane * 16;
     const uint32_t act_row_bytes = p.pass_k * 2 + 16;   // +16: consecutive rows land in different bank groups
+
+    // Launched with AFB_FLAG_PDL this kernel may run while its predecessor on the stream is still at work.  Its successor may
+    // start at once (it, too, begins with weights only); this kernel itself waits for the predecessor below, after its first
+    // ring fill, before it touches activations, the workspace or C.  Without the launch attribute both are no-ops.
+    grid_dependents_may_start();
+    bool dependency_met = false;
 
     // Shared-memory address of this lane's staged activations.  Rows beyond m are never staged: such a lane reads
     // row 0 instead, which only feeds output columns (activation rows) that are never stored.
@@ -129,10 +141,20 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
     const size_t sc_ia = (size_t)(ok_a ? row_a : 0) * groups_per_row, sc_ib = (size_t)(ok_b ? row_b : 0) * groups_per_row;
     uint32_t sc_k = ks + wk * CH;            // k of the chunk whose scales are fetched next
     const uint32_t sc_kstep = wk_count * CH;
-    auto load_group_scales = [&](float& sa, float& sb) {
+    // zero-points of this lane's two channels, as the packed-bf16 constants the unpack subtracts (dequant.cuh)
+    uint32_t z_a = 0u, z_b = 0u;                             // int8 (ZP instances): the decoded zero
+    uint32_t sub_a = 0x43084308u, sub_b = 0x43084308u;       // int4: 136 + the decoded zero
+    uint32_t z_a_nxt = 0u, z_b_nxt = 0u, sub_a_nxt = 0x43084308u, sub_b_nxt = 0x43084308u;
+    auto load_zeros = [&](size_t ia, size_t ib, uint32_t& za, uint32_t& zb, uint32_t& sa4, uint32_t& sb4) {
+        if (BITS == 8) { if (ZP) { za = zero8_const(p.zero[ia], p.enc); zb = zero8_const(p.zero[ib], p.enc); } }
+        else if (p.zero) { sa4 = zero4_const(p.zero[ia], p.enc); sb4 = zero4_const(p.zero[ib], p.enc); }
+    };
+    if (!GROUPED) load_zeros(ok_a ? row_a : 0, ok_b ? row_b : 0, z_a, z_b, sub_a, sub_b);
+    auto load_group_scales = [&](float& sa, float& sb, uint32_t& za, uint32_t& zb, uint32_t& sa4, uint32_t& sb4) {
         const uint32_t grp = sc_k >> p.group_shift;
         if (p.scale_dtype == AFB_SCALE_BF16) { sa = bf16_to_f32(sc_h[sc_ia + grp]); sb = bf16_to_f32(sc_h[sc_ib + grp]); }
         else { sa = sc_f[sc_ia + grp]; sb = sc_f[sc_ib + grp]; }
+        load_zeros(sc_ia + grp, sc_ib + grp, za, zb, sa4, sb4);
         sc_k += sc_kstep;
     };
 
@@ -143,7 +165,8 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
         cp_async_commit();
     }
     float sc_a = 0.f, sc_b = 0.f, sc_a_nxt = 0.f, sc_b_nxt = 0.f;
-    if (GROUPED && my_chunks) load_group_scales(sc_a, sc_b);
+    if (GROUPED && my_chunks) load_group_scales(sc_a, sc_b, z_a, z_b, sub_a, sub_b);
+    if (!dependency_met) { grid_dependency_wait(); dependency_met = true; }   // so far only B, scales and zero-points were read
 
     uint32_t i = 0;   // chunks this warp has consumed
     for (uint32_t pk = ks; pk < kend; pk += p.pass_k) {
@@ -155,7 +178,9 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
                 for (uint32_t pc = tid & 63; pc < pieces; pc += 64) {
                     const uint4 v = ldg_act(p.a + (size_t)r * p.lda + pk + pc * 8);
                     uint4 o;
-                    if (BITS == 8) {  // {k0,k2},{k1,k3},{k4,k6},{k5,k7}
+                    if (p.packed) {   // pre-packed weights unpack to consecutive k: the activations are used as they lie
+                        o = v;
+                    } else if (BITS == 8) {  // {k0,k2},{k1,k3},{k4,k6},{k5,k7}
                         o.x = prmt(v.x, v.y, 0x5410u); o.y = prmt(v.x, v.y, 0x7632u);
                         o.z = prmt(v.z, v.w, 0x5410u); o.w = prmt(v.z, v.w, 0x7632u);
                     } else {          // {k0,k4},{k1,k5},{k2,k6},{k3,k7}
@@ -172,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
         for (uint32_t cl = wk; cl < chunks_in_pass; cl += wk_count, ++i, chunk_off += wk_count * (CH * 2)) {
             if (issued < my_chunks) issue();
             cp_async_commit();
-            if (GROUPED && i + 1 < my_chunks) load_group_scales(sc_a_nxt, sc_b_nxt);
+            if (GROUPED && i + 1 < my_chunks) load_group_scales(sc_a_nxt, sc_b_nxt, z_a_nxt, z_b_nxt, sub_a_nxt, sub_b_nxt);
             // this lane's activations of the chunk: rows g (and g + 8), k = cl*CH + tig*LK ..
             const uint32_t par = BITS == 8 ? ((cl & 1u) << 5) : 0u;   // int8: odd chunks have bit 3 of the piece index set
             uint32_t s[MT][AV * 4];
@@ -199,13 +224,14 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
                     uint32_t a0, a1, a2, a3;
                     s8x4_to_bf16_strided(wav[j] ^ xormask, a0, a2);
                     s8x4_to_bf16_strided(wbv[j] ^ xormask, a1, a3);
+                    if (ZP) { a0 = bf16x2_sub(a0, z_a); a2 = bf16x2_sub(a2, z_a); a1 = bf16x2_sub(a1, z_b); a3 = bf16x2_sub(a3, z_b); }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
                         mma_bf16(GROUPED ? part[mt] : acc[mt], a0, a1, a2, a3, s[mt][2 * j], s[mt][2 * j + 1]);
                 } else {
                     uint32_t qa[4], qb[4];
-                    s4x8_to_bf16_strided(wav[j], magic4, qa);
-                    s4x8_to_bf16_strided(wbv[j], magic4, qb);
+                    s4x8_to_bf16_strided(wav[j], magic4, qa, sub_a);
+                    s4x8_to_bf16_strided(wbv[j], magic4, qb, sub_b);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         mma_bf16(GROUPED ? part[mt] : acc[mt], qa[0], qb[0], qa[1], qb[1], s[mt][4 * j], s[mt][4 * j + 1]);
@@ -220,6 +246,7 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
                     acc[mt][2] = fmaf(sc_b, part[mt][2], acc[mt][2]); acc[mt][3] = fmaf(sc_b, part[mt][3], acc[mt][3]);
                 }
                 sc_a = sc_a_nxt; sc_b = sc_b_nxt;
+                z_a = z_a_nxt; z_b = z_b_nxt; sub_a = sub_a_nxt; sub_b = sub_b_nxt;
             }
         }
     }
@@ -238,45 +265,58 @@ __global__ void __launch_bounds__(kThreads, (BITS == 4 && GROUPED) ? (MT == 1 ? 
     decode_finish<GROUPED>(p, s_red, s_last, cb, nblk, wk_count, MCOLS, cta_of);
     if (u < u_end) __syncthreads();   // the next piece reuses the ring (= the reduction buffer) and the flag word
     }   // pieces of work
+    if (!dependency_met) grid_dependency_wait();
 }
 
-template <int BITS, int MT, bool GROUPED>
-cudaError_t launch_one(const DecodeParams& p, dim3 grid, cudaStream_t s) {
-    auto kern = decode_kernel<BITS, MT, GROUPED>;
+template <int BITS, int MT, bool GROUPED, bool ZP, int RING>
+cudaError_t launch_one(const DecodeParams& p, dim3 grid, bool pdl, cudaStream_t s) {
+    auto kern = decode_kernel<BITS, MT, GROUPED, ZP, RING>;
     static DeviceOnce attr_set;   // per template instance
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set.done(dev)) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT, RING));
         if (e != cudaSuccess) return e;
         attr_set.mark(dev);
     }
-    kern<<<grid, kThreads, smem_bytes(MT), s>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem_bytes(MT, RING); cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 // CTAs of one kernel instance that fit an SM at the same time (asked once per instance and device).
-template <int BITS, int MT, bool GROUPED>
+template <int BITS, int MT, bool GROUPED, int RING>
 int resident_one() {
     static std::atomic<int> cached[32];   // 0 = not asked yet (zero-initialised)
     int dev = 0;
     cudaGetDevice(&dev);
     int n = cached[dev & 31].load(std::memory_order_acquire);
     if (n == 0) {
-        auto kern = decode_kernel<BITS, MT, GROUPED>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT)) != cudaSuccess) return 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem_bytes(MT)) != cudaSuccess) return 0;
+        auto kern = decode_kernel<BITS, MT, GROUPED, false, RING>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT, RING)) != cudaSuccess) return 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem_bytes(MT, RING)) != cudaSuccess) return 0;
         cached[dev & 31].store(n, std::memory_order_release);
     }
     return n;
 }
-int resident_ctas(uint32_t bits, int mt, bool grouped) {
+int resident_ctas(uint32_t bits, int mt, bool grouped) {   // of the 4-stage instances (the 8-stage ones are only used when every CTA is resident anyway)
     if (bits == 8) {
-        if (mt == 1) return grouped ? resident_one<8, 1, true>() : resident_one<8, 1, false>();
-        return grouped ? resident_one<8, 2, true>() : resident_one<8, 2, false>();
+        if (mt == 1) return grouped ? resident_one<8, 1, true, 4>() : resident_one<8, 1, false, 4>();
+        return grouped ? resident_one<8, 2, true, 4>() : resident_one<8, 2, false, 4>();
     }
-    if (mt == 1) return grouped ? resident_one<4, 1, true>() : resident_one<4, 1, false>();
-    return grouped ? resident_one<4, 2, true>() : resident_one<4, 2, false>();
+    if (mt == 1) return grouped ? resident_one<4, 1, true, 4>() : resident_one<4, 1, false, 4>();
+    return grouped ? resident_one<4, 2, true, 4>() : resident_one<4, 2, false, 4>();
+}
+
+template <int BITS, int MT, bool GROUPED>
+cudaError_t launch_cfg(const DecodeParams& p, dim3 grid, bool deep_ring, bool pdl, cudaStream_t s) {
+    const bool zp = BITS == 8 && p.zero != nullptr;
+    if (deep_ring) return zp ? launch_one<BITS, MT, GROUPED, BITS == 8, 8>(p, grid, pdl, s) : launch_one<BITS, MT, GROUPED, false, 8>(p, grid, pdl, s);
+    return zp ? launch_one<BITS, MT, GROUPED, BITS == 8, 4>(p, grid, pdl, s) : launch_one<BITS, MT, GROUPED, false, 4>(p, grid, pdl, s);
 }
 
 }  // namespace
@@ -298,9 +338,8 @@ bool decode_supports(const afb_gemm_args& a) {
 //   * wr: activations are re-read by every column of CTAs, so more activation rows ask for more channels per CTA
 //     (keeps the activation traffic through L2 below about half of the weight traffic);
 //   * slices: only when the channel dimension alone cannot fill the GPU.
-// `stream`: the streaming form (decode_stream.cu): a pass of K need not be whole rounds of the WK warps there.
-static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, bool stream, size_t act_cap,
-                       DecodeParams& p) {
+static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, DecodeParams& p) {
+    const size_t act_cap = (size_t)act_bytes(a.m <= 8 ? 1 : 2);
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
     const uint32_t sms = (uint32_t)sm_count;
     const uint32_t act_bytes_per_k = 2 * a.m;                      // per k, per column of CTAs
@@ -312,7 +351,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, si
     // small matrices with 9 to 16 rows: when 16-channel CTAs alone fill the GPU, they beat wider CTAs with K-slices (no workspace
     // round trip; measured on 4096 x 4096: 10.2 vs 12.4 us at m = 9, 11.9 vs 12.6 at m = 12, equal at m = 16)
     if (weight_mb < 48.0 && a.m > 8 && ctas(1) >= sms * 3 / 2 && (size_t)a.m * (ch * kWarps * 2 + 16) <= act_cap) wr = 1;
-    while (!stream && wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > act_cap) wr *= 2;   // one round of the WK warps must fit the staging area
+    while (wr < 8 && (size_t)a.m * (ch * (kWarps / wr) * 2 + 16) > act_cap) wr *= 2;   // one round of the WK warps must fit the staging area
     // the balanced form (below) pays off for more than 8 activation rows on large matrices (measured: 8 to 25 % there, a loss
     // of up to 10 % for m <= 8, whose grid form needs no K-slices); it runs best with the widest CTA
     bool want_balanced = weight_mb >= 48.0 && a.m > 8;
@@ -326,7 +365,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, si
     if (ctas(wr) > counter_count) s = 1;
     if (const char* e = getenv("AFB_DECODE_WR")) {       // tuning aid: force the CTA shape when it is legal
         const uint32_t v = (uint32_t)atoi(e);
-        if ((v == 1 || v == 2 || v == 4 || v == 8) && (stream || (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= act_cap)) wr = v;
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && (size_t)a.m * (ch * (kWarps / v) * 2 + 16) <= act_cap) wr = v;
     }
     if (const char* e = getenv("AFB_DECODE_SLICES")) {   // tuning aid: force the number of K-slices when it is legal
         const uint32_t v = (uint32_t)atoi(e);
@@ -334,7 +373,7 @@ static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, si
     }
     p.wr = wr; p.slices = s; p.kc = a.k / s;
     // activations staged per pass: as many k as fit the staging area, in whole rounds of the WK warps
-    const uint32_t round = stream ? ch : ch * (kWarps / wr);
+    const uint32_t round = ch * (kWarps / wr);
     uint32_t pass_max = ((uint32_t)act_cap / a.m - 16) / 2 / round * round;   // >= 512 k for m <= 16, round <= 512
     if (pass_max == 0) pass_max = round;
     const uint32_t npass = (p.kc + pass_max - 1) / pass_max;
@@ -385,30 +424,26 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
     p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
     const bool grouped = a.group_size != 0;
     const int mt = a.m <= 8 ? 1 : 2;
-    const bool packed = a.b_layout == AFB_LAYOUT_COL_PACKED;
-    // two forms of the kernel: the streaming form is the default; AFB_DECODE_IMPL=staged selects the other (plain weights only)
-    static const bool env_staged = [] { const char* e = getenv("AFB_DECODE_IMPL"); return e && e[0] == 's' && e[1] == 't' && e[2] == 'a'; }();
-    const bool stream = packed || !env_staged;
-    if (stream) {
-        pick_shape(a, ctx->sm_count, decode_stream_resident(a.b_bits, mt, grouped), ws_bytes, counter_count, true, (size_t)decode_stream_act_bytes(mt), p);
-        p.ws = ws; p.counters = counters;
-        dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
-        if (p.streamk) grid = dim3(p.slices, 1);
-        const cudaError_t e = decode_stream_launch(a.b_bits, mt, grouped, packed, p, grid, (a.flags & AFB_FLAG_PDL) != 0, s);
-        count_launch();
-        return e == cudaSuccess ? AFB_OK : cuda_fail(e);
-    }
-    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, false, (size_t)act_bytes(mt), p);
+    p.packed = a.b_layout == AFB_LAYOUT_COL_PACKED ? 1u : 0u;
+    p.zero = reinterpret_cast<const uint8_t*>(a.ptr_zero);
+    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, p);
     p.ws = ws; p.counters = counters;
     dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
     if (p.streamk) grid = dim3(p.slices, 1);
+    // Deep ring: when a warp owns at most 8 chunks and two CTAs per SM hold the whole grid, all weights of the launch are in
+    // flight at once (small matrices; with AFB_FLAG_PDL they stream in while the preceding kernel finishes).
+    const uint32_t ch = a.b_bits == 8 ? 64 : 128;
+    const uint32_t chunks_per_warp = (p.kc / ch + (kWarps / p.wr) - 1) / (kWarps / p.wr);
+    bool deep_ring = !p.streamk && chunks_per_warp <= 8 && (uint64_t)grid.x * grid.y <= 2ull * (uint64_t)ctx->sm_count;
+    if (const char* e = getenv("AFB_DECODE_DEEP_RING")) deep_ring = atoi(e) != 0 && !p.streamk;   // tuning aid
+    const bool pdl = (a.flags & AFB_FLAG_PDL) != 0;
     cudaError_t e;
     if (a.b_bits == 8) {
-        if (mt == 1) e = grouped ? launch_one<8, 1, true>(p, grid, s) : launch_one<8, 1, false>(p, grid, s);
-        else         e = grouped ? launch_one<8, 2, true>(p, grid, s) : launch_one<8, 2, false>(p, grid, s);
+        if (mt == 1) e = grouped ? launch_cfg<8, 1, true>(p, grid, deep_ring, pdl, s) : launch_cfg<8, 1, false>(p, grid, deep_ring, pdl, s);
+        else         e = grouped ? launch_cfg<8, 2, true>(p, grid, deep_ring, pdl, s) : launch_cfg<8, 2, false>(p, grid, deep_ring, pdl, s);
     } else {
-        if (mt == 1) e = grouped ? launch_one<4, 1, true>(p, grid, s) : launch_one<4, 1, false>(p, grid, s);
-        else         e = grouped ? launch_one<4, 2, true>(p, grid, s) : launch_one<4, 2, false>(p, grid, s);
+        if (mt == 1) e = grouped ? launch_cfg<4, 1, true>(p, grid, deep_ring, pdl, s) : launch_cfg<4, 1, false>(p, grid, deep_ring, pdl, s);
+        else         e = grouped ? launch_cfg<4, 2, true>(p, grid, deep_ring, pdl, s) : launch_cfg<4, 2, false>(p, grid, deep_ring, pdl, s);
     }
     count_launch();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);

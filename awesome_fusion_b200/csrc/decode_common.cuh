@@ -1,5 +1,4 @@
-// Pieces shared by the two forms of the decode kernel (decode.cu: activations staged in the weights' pairing by the CTA;
-// decode_stream.cu: activations copied as they are, deeper weight ring, optional programmatic dependent launch).
+// Parameter block, small PTX wrappers and the end-of-piece reduction of the decode kernel (decode.cu).
 #pragma once
 #include "afb_internal.h"
 #include "dequant.cuh"
@@ -15,9 +14,11 @@ struct DecodeParams {
     const uint16_t* a;
     const uint8_t* b;
     const void* scale;
+    const uint8_t* zero;   // optional zero-points (nullptr = none), one byte per scale entry
     uint16_t* c;
     uint32_t m, n, k, lda, ldb_bytes, ldc;
     uint32_t enc, scale_dtype, group;
+    uint32_t packed;  // B is in the pre-packed order of afb_prepack: the unpack yields consecutive k, activations are staged as they lie
     uint32_t wr;      // warps along the channel dimension (1, 2, 4 or 8); WK = 8 / wr
     uint32_t kc;      // k elements per slice (multiple of the chunk)
     uint32_t pass_k;  // k elements staged per pass (m * (pass_k * 2 + 16) <= the activation buffer)
@@ -120,10 +121,5 @@ __device__ __forceinline__ void decode_finish(const DecodeParams& p, const float
         }
     }
 }
-
-// the streaming form (decode_stream.cu)
-int decode_stream_act_bytes(int mt);
-int decode_stream_resident(uint32_t bits, int mt, bool grouped);
-cudaError_t decode_stream_launch(uint32_t bits, int mt, bool grouped, bool packed, const DecodeParams& p, dim3 grid, bool pdl, cudaStream_t s);
 
 }  // namespace afb

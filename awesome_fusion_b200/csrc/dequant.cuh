@@ -11,6 +11,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include "afb_capi.h"
 
 namespace afb {
 
@@ -74,23 +75,24 @@ __device__ __forceinline__ void s8x4_to_bf16_strided(uint32_t w, uint32_t& p02, 
 
 // magic = 0x43084308 for two's-complement nibbles, 0x43004300 for offset-binary (+8) nibbles.
 // x holds two nibbles in bits [0,4) and [16,20) (other bits ignored) -> two exact bf16.
-__device__ __forceinline__ uint32_t s4pair_to_bf16x2(uint32_t x, uint32_t magic) {
-    return bf16x2_sub(lop3_and_xor(x, 0x000f000fu, magic), 0x43084308u);  // - 136
+// `sub` is the packed-bf16 constant that is subtracted: 136 without zero-points, 136 + zero with them (the same instruction).
+__device__ __forceinline__ uint32_t s4pair_to_bf16x2(uint32_t x, uint32_t magic, uint32_t sub = 0x43084308u) {
+    return bf16x2_sub(lop3_and_xor(x, 0x000f000fu, magic), sub);
 }
 // Eight consecutive nibbles of w (k0 in bits [0,4)) -> {k0,k1},{k2,k3},{k4,k5},{k6,k7}.
-__device__ __forceinline__ void s4x8_to_bf16_natural(uint32_t w, uint32_t magic, uint32_t p[4]) {
+__device__ __forceinline__ void s4x8_to_bf16_natural(uint32_t w, uint32_t magic, uint32_t p[4], uint32_t sub = 0x43084308u) {
     const uint32_t sh = w >> 4;
-    p[0] = s4pair_to_bf16x2(prmt(w, sh, 0x0400u), magic);
-    p[1] = s4pair_to_bf16x2(prmt(w, sh, 0x0501u), magic);
-    p[2] = s4pair_to_bf16x2(prmt(w, sh, 0x0602u), magic);
-    p[3] = s4pair_to_bf16x2(prmt(w, sh, 0x0703u), magic);
+    p[0] = s4pair_to_bf16x2(prmt(w, sh, 0x0400u), magic, sub);
+    p[1] = s4pair_to_bf16x2(prmt(w, sh, 0x0501u), magic, sub);
+    p[2] = s4pair_to_bf16x2(prmt(w, sh, 0x0602u), magic, sub);
+    p[3] = s4pair_to_bf16x2(prmt(w, sh, 0x0703u), magic, sub);
 }
 // Cheaper pairing: {k0,k4},{k1,k5},{k2,k6},{k3,k7}.
-__device__ __forceinline__ void s4x8_to_bf16_strided(uint32_t w, uint32_t magic, uint32_t p[4]) {
-    p[0] = s4pair_to_bf16x2(w, magic);
-    p[1] = s4pair_to_bf16x2(w >> 4, magic);
-    p[2] = s4pair_to_bf16x2(w >> 8, magic);
-    p[3] = s4pair_to_bf16x2(w >> 12, magic);
+__device__ __forceinline__ void s4x8_to_bf16_strided(uint32_t w, uint32_t magic, uint32_t p[4], uint32_t sub = 0x43084308u) {
+    p[0] = s4pair_to_bf16x2(w, magic, sub);
+    p[1] = s4pair_to_bf16x2(w >> 4, magic, sub);
+    p[2] = s4pair_to_bf16x2(w >> 8, magic, sub);
+    p[3] = s4pair_to_bf16x2(w >> 12, magic, sub);
 }
 
 // Consecutive-k pairs {k0,k1},{k2,k3} of a word, whichever way the word is laid out: plain [k0,k1,k2,k3] needs two byte
@@ -99,9 +101,21 @@ __device__ __forceinline__ void s8x4_to_bf16_pairs(uint32_t w, bool packed, uint
     if (packed) s8x4_to_bf16_strided(w, p01, p23);
     else s8x4_to_bf16_natural(w, p01, p23);
 }
-__device__ __forceinline__ void s4x8_to_bf16_pairs(uint32_t w, uint32_t magic, bool packed, uint32_t p[4]) {
-    if (packed) s4x8_to_bf16_strided(w, magic, p);
-    else s4x8_to_bf16_natural(w, magic, p);
+__device__ __forceinline__ void s4x8_to_bf16_pairs(uint32_t w, uint32_t magic, bool packed, uint32_t p[4], uint32_t sub = 0x43084308u) {
+    if (packed) s4x8_to_bf16_strided(w, magic, p, sub);
+    else s4x8_to_bf16_natural(w, magic, p, sub);
+}
+// Zero-points: a byte in the weights' own encoding -> the packed-bf16 constant the unpack subtracts.
+//   int8: the decoded zero itself, both halves (one extra sub.bf16x2 per pair; |q - z| <= 255 is exact in bf16);
+//   int4: 136 + decoded zero, which takes the place of the 136 the unpack subtracts anyway (no extra instruction).
+__device__ __forceinline__ uint32_t zero8_const(uint32_t zbyte, uint32_t enc) {
+    const int z = enc == AFB_ENC_OFFSET_BINARY ? (int)zbyte - 128 : (int)(int8_t)zbyte;
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)z)) * 0x00010001u;
+}
+__device__ __forceinline__ uint32_t zero4_const(uint32_t zbyte, uint32_t enc) {
+    const int nib = (int)(zbyte & 0xFu);
+    const int z = enc == AFB_ENC_OFFSET_BINARY ? nib - 8 : ((nib ^ 8) - 8);
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)(136 + z))) * 0x00010001u;
 }
 // Place of weight k inside its word in the pre-packed layout (int8: bytes [k0,k2,k1,k3]; int4: nibbles [k0,k2,k4,k6,k1,k3,k5,k7]).
 __host__ __device__ __forceinline__ uint32_t packed_pos(uint32_t bits, uint32_t k) {

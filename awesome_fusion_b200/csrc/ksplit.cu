@@ -324,11 +324,12 @@ extern "C" int afb_gemm_launch_tiles(const afb_gemm_args* args, uint32_t* tile_d
     return launch_prefill_ts_tiles(*args, ctx, tile_done, (cudaStream_t)stream);
 }
 
-extern "C" int afb_abi_sizes(uint32_t sizes[3]) {
+extern "C" int afb_abi_sizes(uint32_t sizes[4]) {
     if (!sizes) return AFB_ERR_BAD_ARG;
     sizes[0] = (uint32_t)sizeof(afb_gemm_args);
     sizes[1] = (uint32_t)sizeof(afb_allreduce_args);
     sizes[2] = (uint32_t)sizeof(afb_tile_allreduce_args);
+    sizes[3] = (uint32_t)sizeof(afb_fused_args);
     return AFB_OK;
 }
 

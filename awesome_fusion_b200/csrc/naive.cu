@@ -30,6 +30,13 @@ __device__ __forceinline__ float load_q(const uint8_t* __restrict__ b, uint32_t 
     return (float)v;
 }
 
+// decoded zero-point (a byte in the weights' own encoding)
+__device__ __forceinline__ float decode_zero(uint8_t z, uint32_t bits, uint32_t enc) {
+    if (bits == 8) return (float)(enc == AFB_ENC_OFFSET_BINARY ? (int)z - 128 : (int)(int8_t)z);
+    const uint32_t nib = z & 0xFu;
+    return (float)(enc == AFB_ENC_OFFSET_BINARY ? (int)nib - 8 : (int)(nib ^ 8u) - 8);
+}
+
 __device__ __forceinline__ float load_scale(const void* __restrict__ s, size_t idx, uint32_t dtype) {
     return dtype == AFB_SCALE_BF16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(s)[idx])
                                    : reinterpret_cast<const float*>(s)[idx];
@@ -42,12 +49,16 @@ __global__ void __launch_bounds__(256) naive_gemm_kernel(afb_gemm_args a) {
     const uint16_t* __restrict__ pa = reinterpret_cast<const uint16_t*>(a.ptr_a) + (size_t)m * a.lda;
     const uint8_t* __restrict__ pb = reinterpret_cast<const uint8_t*>(a.ptr_b);
     const uint32_t groups = a.group_size ? a.k / a.group_size : 0;
+    const uint8_t* __restrict__ pz = reinterpret_cast<const uint8_t*>(a.ptr_zero);
     float scale = a.group_size ? 0.f : load_scale(a.ptr_scale, n, a.scale_dtype);
+    float zero = (pz && !a.group_size) ? decode_zero(pz[n], a.b_bits, a.b_encoding) : 0.f;
     float acc = 0.f;
     for (uint32_t k = 0; k < a.k; ++k) {
-        if (a.group_size && (k % a.group_size) == 0)
+        if (a.group_size && (k % a.group_size) == 0) {
             scale = load_scale(a.ptr_scale, (size_t)n * groups + k / a.group_size, a.scale_dtype);
-        const float q = load_q(pb, n, k, a.ldb, a.b_bits, a.b_encoding, a.b_layout);
+            if (pz) zero = decode_zero(pz[(size_t)n * groups + k / a.group_size], a.b_bits, a.b_encoding);
+        }
+        const float q = load_q(pb, n, k, a.ldb, a.b_bits, a.b_encoding, a.b_layout) - zero;
         const float w = __fmul_rn(q, scale);
         acc = __fadd_rn(acc, __fmul_rn(bf16_bits_to_f32(pa[k]), w));
     }
@@ -86,6 +97,11 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
             const size_t row_bytes = a.b_bits == 8 ? (size_t)a.ldb : (size_t)(a.ldb >> 1);
             const uint4 raw = *reinterpret_cast<const uint4*>(pb + (size_t)n * row_bytes + (a.b_bits == 8 ? k0 : (k0 >> 1)));
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint8_t* pz = reinterpret_cast<const uint8_t*>(a.ptr_zero);
+            const uint32_t zb = pz ? pz[a.group_size ? (size_t)n * groups + k0 / a.group_size : n] : 0u;
+            const bool has_zero = pz != nullptr;
+            const uint32_t z8 = zero8_const(has_zero ? zb : (a.b_encoding == AFB_ENC_OFFSET_BINARY ? 128u : 0u), a.b_encoding);
+            const uint32_t sub4 = has_zero ? zero4_const(zb, a.b_encoding) : 0x43084308u;
             uint32_t sc = 0;
             if (a.group_size) {
                 // a 16-byte piece never straddles a group (group_size is a multiple of 32)
@@ -105,11 +121,12 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
                     if (a.b_bits == 8) {
                         uint32_t p02, p13;
                         s8x4_to_bf16_strided(w[j] ^ xormask, p02, p13);
+                        if (has_zero) { p02 = bf16x2_sub(p02, z8); p13 = bf16x2_sub(p13, z8); }
                         o16[4 * j + 0] = (uint16_t)(p02 & 0xffff); o16[4 * j + 2] = (uint16_t)(p02 >> 16);
                         o16[4 * j + 1] = (uint16_t)(p13 & 0xffff); o16[4 * j + 3] = (uint16_t)(p13 >> 16);
                     } else {
                         uint32_t p[4];
-                        s4x8_to_bf16_strided(w[j], magic4, p);
+                        s4x8_to_bf16_strided(w[j], magic4, p, sub4);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) { o16[8 * j + i] = (uint16_t)(p[i] & 0xffff); o16[8 * j + 4 + i] = (uint16_t)(p[i] >> 16); }
                     }
@@ -121,6 +138,7 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
                 for (int j = 0; j < 4; ++j) {
                     uint32_t p01, p23;
                     s8x4_to_bf16_pairs(w[j] ^ xormask, packed, p01, p23);
+                    if (has_zero) { p01 = bf16x2_sub(p01, z8); p23 = bf16x2_sub(p23, z8); }
                     if (a.group_size) { p01 = bf16x2_mul(p01, sc); p23 = bf16x2_mul(p23, sc); }
                     o[2 * j] = p01; o[2 * j + 1] = p23;
                 }
@@ -128,7 +146,7 @@ __global__ void __launch_bounds__(256) dequant_dump_kernel(afb_gemm_args a, uint
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t p[4];
-                    s4x8_to_bf16_pairs(w[j], magic4, packed, p);
+                    s4x8_to_bf16_pairs(w[j], magic4, packed, p, sub4);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) o[4 * j + i] = a.group_size ? bf16x2_mul(p[i], sc) : p[i];
                 }
@@ -158,7 +176,7 @@ int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s) {
         if (a.k % per16 || (a.b_bits == 8 ? a.ldb % 16 : a.ldb % 32)) return AFB_ERR_UNSUPPORTED;
         if (a.group_size && a.group_size % 32) return AFB_ERR_UNSUPPORTED;
     } else {
-        if (a.b_bits != 8 || a.n % 4 || a.ldb % 4 || a.group_size) return AFB_ERR_UNSUPPORTED;
+        if (a.b_bits != 8 || a.n % 4 || a.ldb % 4 || a.group_size || a.ptr_zero) return AFB_ERR_UNSUPPORTED;
     }
     if ((uintptr_t)a.ptr_b % 16) return AFB_ERR_BAD_ARG;
     dequant_dump_kernel<<<296, 256, 0, s>>>(a, reinterpret_cast<uint16_t*>(out));

@@ -392,14 +392,17 @@ bool prefill_supports(const afb_gemm_args& a) {
     if (ld_bytes % 16) return false;
     if ((uintptr_t)a.ptr_a % 16 || (uintptr_t)a.ptr_b % 16 || (uintptr_t)a.ptr_c % 16 || (uintptr_t)a.ptr_scale % 16) return false;
     if (a.group_size) {
-        if (a.group_size % BK || a.k % a.group_size) return false;
+        if (a.group_size % 32 || a.k % a.group_size) return false;   // the tensor-memory form converts 32 consecutive k per thread
         if (a.scale_dtype != AFB_SCALE_BF16) return false;  // the dequant contract is bf16_rn(q * bf16 scale)
     }
     return true;
 }
 
+// What only the tensor-memory form (prefill_ts.cu) covers: groups of 32 (this form converts 64-wide steps), zero-points.
+bool prefill_needs_ts(const afb_gemm_args& a) { return (a.group_size && a.group_size % BK) || a.ptr_zero != nullptr; }
+
 int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
-    if (!prefill_supports(a)) return AFB_ERR_UNSUPPORTED;
+    if (!prefill_supports(a) || prefill_needs_ts(a)) return AFB_ERR_UNSUPPORTED;
     const bool grouped = a.group_size != 0;
     // BN = 256 halves the A traffic per flop; BN = 128 wastes less on narrow N
     const bool wide = a.n > 128;

@@ -39,6 +39,7 @@ constexpr int kThreadsFwd = kThreads + 32 * kFwdWarps;
 struct TsParams {
     uint16_t* c;
     const void* scale;
+    const uint8_t* zero;   // optional zero-points (nullptr = none): one byte per scale entry, in the weights' own encoding
     uint32_t m, n, k, ldc;
     uint32_t enc, scale_dtype, group;
     uint32_t m_tiles, n_tiles;
@@ -57,6 +58,13 @@ struct TsParams {
     uint32_t tail_first, tail_tiles, tail_parts;
     float* tail_ws;
     uint32_t* tail_counters;   // one per tail tile, zero on entry, zero again on exit
+    // optional fused epilogue (bf16 output only): v = acc * scale + bias[channel]; gated: rows 2i / 2i+1 of B are the gate / up
+    // projection of output channel i and C[m,i] = act(v_gate) * v_up, else C[m,n] = act(v); then + residual[m, channel]; one rounding
+    const float* bias;
+    const uint16_t* residual;
+    uint32_t ld_res;
+    uint32_t fused;        // 0: off; bit 0: on; bit 1: gated
+    uint32_t act;          // AFB_ACT_*
     uint32_t push_rows, push_rank;
     uint32_t push_on;      // 0: off; 1: the epilogue stores to the owner directly; 2: the epilogue stores to p.c (local) and the
                            // forwarder warps copy each finished tile to its owner while the next tile is being computed
@@ -250,7 +258,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
         const bool packed = p.packed != 0;
         const uint32_t groups_per_row = GROUPED ? p.k / p.group : 0;
-        const uint32_t kb_per_group = GROUPED ? p.group / BK : 1;
+        const bool has_zero = p.zero != nullptr;
         // raw tile in shared memory: rows of 64 (int8) / 32 (int4) bytes, stored by TMA with the 64- / 32-byte swizzle
         // (16-byte piece index XOR row bits); this thread converts kKPer consecutive k of its row
         constexpr int kRawPer = kKPer * BITS / 8;                 // bytes per thread and stage: 32/16 (int8), 16/8 (int4)
@@ -272,14 +280,33 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             tile_coords(p, t, mt_, nt_);
             const uint32_t m0 = mt_ * BMA, n0 = nt_ * BNW;
             const uint32_t nn = n0 + ch;
-            uint32_t sc_cur = 0, sc_nxt = 0;
-            auto load_gscale = [&](uint32_t gidx) -> uint32_t {
-                if (nn >= p.n || gidx >= groups_per_row) return (uint32_t)0;
-                return bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
+            // Scale (and zero-point) of the group this thread's kKPer consecutive k of the step lie in (groups are multiples of kKPer,
+            // so a thread never straddles one).  The next group's values are fetched one group ahead.
+            uint32_t sc_cur = 0, sc_nxt = 0, zb_cur = 0, zb_nxt = 0;
+            auto load_group = [&](uint32_t gidx, uint32_t& sc, uint32_t& zb) {
+                sc = 0; zb = 0;
+                if (nn >= p.n || gidx >= groups_per_row) return;
+                sc = bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
+                if (has_zero) zb = p.zero[(size_t)nn * groups_per_row + gidx];
             };
-            if (GROUPED) sc_nxt = load_gscale(w.kb0 / kb_per_group);   // a stretch of K starts on a group boundary
-            for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
-                if (GROUPED && (kb % kb_per_group) == 0) { sc_cur = sc_nxt; sc_nxt = load_gscale(kb / kb_per_group + 1); }
+            uint32_t kpos = w.kb0 * BK + kq * kKPer;            // first k this thread converts in the coming step
+            const uint32_t gstep = (GROUPED && p.group < (uint32_t)BK) ? BK / p.group : 1u;   // groups a 64-wide step advances by (2 for groups of 32)
+            uint32_t gcur = GROUPED ? kpos / p.group : 0, gend = GROUPED ? (gcur + 1) * p.group : 0xffffffffu;
+            uint32_t z8 = 0u, sub4 = 0x43084308u;               // zero-point constants of the unpack (dequant.cuh)
+            if (GROUPED) {
+                load_group(gcur, sc_cur, zb_cur);
+                load_group(gcur + gstep, sc_nxt, zb_nxt);
+            } else if (has_zero && nn < p.n) {
+                zb_cur = p.zero[nn];
+            }
+            if (has_zero) { if (BITS == 8) z8 = zero8_const(zb_cur, p.enc); else sub4 = zero4_const(zb_cur, p.enc); }
+            for (uint32_t kb = w.kb0; kb < w.kb1; ++kb, kpos += BK) {
+                if (GROUPED && kpos >= gend) {
+                    gcur += gstep; gend += gstep * p.group;
+                    sc_cur = sc_nxt; zb_cur = zb_nxt;
+                    load_group(gcur + gstep, sc_nxt, zb_nxt);
+                    if (has_zero) { if (BITS == 8) z8 = zero8_const(zb_cur, p.enc); else sub4 = zero4_const(zb_cur, p.enc); }
+                }
                 const bool two_terms = GROUPED && p.exact;
                 if (!wait_or_abort(bar_full(st), ph, abort_flag) || !wait_or_abort(bar_empty_a(sa), pa ^ 1u, abort_flag) ||
                     (two_terms && !wait_or_abort(bar_empty_a(sa + 1), pa ^ 1u, abort_flag))) {
@@ -305,9 +332,10 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 for (int j = 0; j < kWords; ++j) {
                     if (BITS == 8) {
                         s8x4_to_bf16_pairs(w[j] ^ xormask, packed, o[2 * j], o[2 * j + 1]);
+                        if (has_zero) { o[2 * j] = bf16x2_sub(o[2 * j], z8); o[2 * j + 1] = bf16x2_sub(o[2 * j + 1], z8); }
                     } else {
                         uint32_t qv[4];
-                        s4x8_to_bf16_pairs(w[j], magic4, packed, qv);
+                        s4x8_to_bf16_pairs(w[j], magic4, packed, qv, sub4);
                         o[4 * j] = qv[0]; o[4 * j + 1] = qv[1]; o[4 * j + 2] = qv[2]; o[4 * j + 3] = qv[3];
                     }
                 }
@@ -364,6 +392,28 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                     float* wsp = p.tail_ws + ((size_t)(w.tail_r * p.tail_parts + w.part) * BMA + col) * BNW + ch;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) __stcg(wsp + (size_t)j * BNW, __uint_as_float(r[j]));
+                } else if (p.fused) {
+                    // every lane takes part (the gated form exchanges values between the two lanes of a pair): range checks only guard the accesses
+                    const uint32_t mrow = m0 + col;
+                    const bool gated = (p.fused & 2u) != 0;
+                    const float bias = (p.bias && nn < p.n) ? p.bias[nn] : 0.f;
+                    const uint32_t nout = gated ? (nn >> 1) : nn;
+                    const bool writer = nn < p.n && (!gated || (lane & 1) == 0);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = fmaf(__uint_as_float(r[j]), scale, bias);
+                        if (gated) {   // even lane: gate, odd lane: up
+                            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                            if (p.act == AFB_ACT_SILU) v = v / (1.f + __expf(-v));
+                            v *= other;
+                        } else if (p.act == AFB_ACT_SILU) {
+                            v = v / (1.f + __expf(-v));
+                        }
+                        if (writer && mrow + j < p.m) {
+                            if (p.residual) v += __uint_as_float((uint32_t)p.residual[(size_t)(mrow + j) * p.ld_res + nout] << 16);
+                            p.c[(size_t)(mrow + j) * p.ldc + nout] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+                        }
+                    }
                 } else if (nn < p.n) {
                     const uint32_t mrow = m0 + col;
                     if (p.c_f32) {
@@ -546,7 +596,7 @@ uint32_t pick_group_m(const afb_gemm_args& a, uint32_t m_tiles, uint32_t n_tiles
 
 template <int BITS, bool GROUPED, int BMA>
 int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr, void* const* push = nullptr,
-                  uint32_t push_world = 0, uint32_t push_rank = 0, bool push_via_local = false) {
+                  uint32_t push_world = 0, uint32_t push_rank = 0, bool push_via_local = false, const afb_fused_args* fused = nullptr) {
     using L = TsLayout<BITS, BMA>;
     static_assert(L::kDynamic <= 232448, "shared memory budget");
     CUtensorMap ta, tw;
@@ -559,6 +609,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     TsParams p;
     p.c = reinterpret_cast<uint16_t*>(a.ptr_c);
     p.scale = a.ptr_scale;
+    p.zero = reinterpret_cast<const uint8_t*>(a.ptr_zero);
     p.m = a.m; p.n = a.n; p.k = a.k; p.ldc = a.ldc;
     p.enc = a.b_encoding; p.scale_dtype = a.scale_dtype; p.group = a.group_size;
     p.m_tiles = (a.m + BMA - 1) / BMA;
@@ -576,11 +627,11 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
         const uint32_t tiles_all = p.m_tiles * p.n_tiles, sms = (uint32_t)ctx->sm_count, nkb = a.k / BK;
         const uint32_t rest = tiles_all > sms ? tiles_all % sms : 0;
         const char* e = getenv("AFB_PREFILL_SPLIT_TAIL");   // tuning aid: 0 switches it off
-        const bool allowed = !(e && atoi(e) == 0) && !tile_done && !push && a.n % 4 == 0;
+        const bool allowed = !(e && atoi(e) == 0) && !tile_done && !push && !fused && a.n % 4 == 0;
         if (allowed && rest > 0 && rest <= sms / 2) {
             uint32_t parts = sms / rest;
             if (parts > 4) parts = 4;
-            const uint32_t kb_group = GROUPED ? a.group_size / BK : 1;
+            const uint32_t kb_group = (GROUPED && a.group_size > (uint32_t)BK) ? a.group_size / BK : 1;
             while (parts >= 2 && (nkb % parts != 0 || (nkb / parts) % kb_group != 0 || nkb / parts < 8)) --parts;
             if (parts >= 2 && (size_t)rest * parts * BMA * BNW * sizeof(float) <= ctx->splitk_ws_bytes && rest <= ctx->splitk_counter_count) {
                 int wrc = AFB_OK;
@@ -591,6 +642,11 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
             }
         }
     }
+    p.bias = fused ? reinterpret_cast<const float*>(fused->ptr_bias) : nullptr;
+    p.residual = fused ? reinterpret_cast<const uint16_t*>(fused->ptr_residual) : nullptr;
+    p.ld_res = fused ? fused->ld_residual : 0;
+    p.fused = fused ? (1u | (fused->gated ? 2u : 0u)) : 0u;
+    p.act = fused ? fused->activation : AFB_ACT_NONE;
     p.push_on = push ? (push_via_local ? 2u : 1u) : 0u;
     // every rank walks the row tiles from a different start, so that at any moment the ranks push to different owners
     // instead of all loading the same peer's NVLink ingress
@@ -639,16 +695,21 @@ int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* 
     return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank, (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) != 0);
 }
 
-int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s) {
-    if (!prefill_supports(a)) return AFB_ERR_UNSUPPORTED;
+// `fused`: optional epilogue description (bias, activation, gate * up, residual); a.ptr_c / a.ldc describe the [M, N_out] result.
+int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, const afb_fused_args* fused) {
+    if (!fused && !prefill_supports(a)) return AFB_ERR_UNSUPPORTED;   // the fused entry point has checked its own argument block
     const bool grouped = a.group_size != 0;
     const bool wide = a.m > 128;   // activation rows per tile: 256, or 128 when M is small
+    uint32_t* const no_tiles = nullptr;
+    void* const* const no_push = nullptr;
+#define AFB_TS_LAUNCH(B, G, W) launch_ts_cfg<B, G, W>(a, ctx, s, no_tiles, no_push, 0, 0, false, fused)
     if (a.b_bits == 8) {
-        if (wide) return grouped ? launch_ts_cfg<8, true, 256>(a, ctx, s) : launch_ts_cfg<8, false, 256>(a, ctx, s);
-        return grouped ? launch_ts_cfg<8, true, 128>(a, ctx, s) : launch_ts_cfg<8, false, 128>(a, ctx, s);
+        if (wide) return grouped ? AFB_TS_LAUNCH(8, true, 256) : AFB_TS_LAUNCH(8, false, 256);
+        return grouped ? AFB_TS_LAUNCH(8, true, 128) : AFB_TS_LAUNCH(8, false, 128);
     }
-    if (wide) return grouped ? launch_ts_cfg<4, true, 256>(a, ctx, s) : launch_ts_cfg<4, false, 256>(a, ctx, s);
-    return grouped ? launch_ts_cfg<4, true, 128>(a, ctx, s) : launch_ts_cfg<4, false, 128>(a, ctx, s);
+    if (wide) return grouped ? AFB_TS_LAUNCH(4, true, 256) : AFB_TS_LAUNCH(4, false, 256);
+    return grouped ? AFB_TS_LAUNCH(4, true, 128) : AFB_TS_LAUNCH(4, false, 128);
+#undef AFB_TS_LAUNCH
 }
 
 }  // namespace afb

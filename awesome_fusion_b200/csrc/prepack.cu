@@ -52,6 +52,17 @@ __global__ void __launch_bounds__(256) prepack_row_kernel(const uint8_t* __restr
     }
 }
 
+// rows of two equally shaped byte matrices interleaved: dst row 2i = g row i, dst row 2i+1 = u row i
+__global__ void __launch_bounds__(256) interleave_rows_kernel(const uint8_t* __restrict__ g, const uint8_t* __restrict__ u, uint8_t* __restrict__ dst,
+                                                              uint32_t rows, uint32_t row_bytes) {
+    const size_t total = (size_t)rows * row_bytes;
+    for (size_t id = blockIdx.x * (size_t)blockDim.x + threadIdx.x; id < total; id += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = id / row_bytes, c = id % row_bytes;
+        dst[(2 * r) * row_bytes + c] = g[id];
+        dst[(2 * r + 1) * row_bytes + c] = u[id];
+    }
+}
+
 }  // namespace
 }  // namespace afb
 
@@ -81,6 +92,38 @@ extern "C" int afb_prepack(const afb_gemm_args* a, void* out_b, uint32_t out_ldb
         prepack_row_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(a->ptr_b), reinterpret_cast<uint8_t*>(out_b), a->n, a->k, a->ldb, out_pitch);
     }
     count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
+extern "C" int afb_prepack_gated(const afb_gemm_args* gate, const void* b_up, const void* scale_up, const void* zero_up, void* out_b,
+                                 uint32_t out_ldb, void* out_scale, void* out_zero, void* stream) {
+    if (!gate || !gate->ptr_b || !gate->ptr_scale || !b_up || !scale_up || !out_b || !out_scale || gate->n == 0 || gate->k == 0) return AFB_ERR_BAD_ARG;
+    if (gate->b_bits != 8 && gate->b_bits != 4) return AFB_ERR_BAD_ARG;
+    if (gate->b_layout != AFB_LAYOUT_COL) return AFB_ERR_UNSUPPORTED;
+    if ((gate->ptr_zero != nullptr) != (zero_up != nullptr) || (gate->ptr_zero && !out_zero)) return AFB_ERR_BAD_ARG;
+    if (gate->group_size && gate->k % gate->group_size) return AFB_ERR_BAD_ARG;
+    const uint32_t per_word = gate->b_bits == 8 ? 4u : 8u;
+    if (gate->k % per_word || out_ldb < gate->k || gate->ldb < gate->k) return AFB_ERR_BAD_ARG;
+    const uint32_t out_pitch = out_ldb * gate->b_bits / 8, in_pitch = gate->ldb * gate->b_bits / 8, row_bytes = gate->k * gate->b_bits / 8;
+    if (out_pitch % 4 || in_pitch % 4 || (uintptr_t)out_b % 4 || (uintptr_t)gate->ptr_b % 4 || (uintptr_t)b_up % 4) return AFB_ERR_BAD_ARG;
+    if (!current_ctx()) return AFB_ERR_NOT_INIT;
+    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t* ob = reinterpret_cast<uint8_t*>(out_b);
+    // the packing kernel with a doubled output pitch writes every other row: gate rows at 2i, up rows at 2i + 1
+    prepack_col_kernel<<<592, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(gate->ptr_b), ob, gate->n, row_bytes, in_pitch, 2 * out_pitch, gate->b_bits);
+    prepack_col_kernel<<<592, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(b_up), ob + out_pitch, gate->n, row_bytes, in_pitch, 2 * out_pitch, gate->b_bits);
+    const uint32_t groups = gate->group_size ? gate->k / gate->group_size : 1;
+    const uint32_t sbytes = groups * (gate->scale_dtype == AFB_SCALE_BF16 ? 2u : 4u);
+    interleave_rows_kernel<<<148, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(gate->ptr_scale), reinterpret_cast<const uint8_t*>(scale_up),
+                                               reinterpret_cast<uint8_t*>(out_scale), gate->n, sbytes);
+    unsigned launches = 3;
+    if (gate->ptr_zero) {
+        interleave_rows_kernel<<<148, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(gate->ptr_zero), reinterpret_cast<const uint8_t*>(zero_up),
+                                                   reinterpret_cast<uint8_t*>(out_zero), gate->n, groups);
+        ++launches;
+    }
+    count_launch(launches);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);
 }

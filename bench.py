@@ -117,9 +117,10 @@ class ClockSampler:
 # device-resident problem instances (torch owns the memory; the kernels are ours, through the C ABI)
 # ----------------------------------------------------------------------------------------
 class Gemm:
-    """One GEMM with synthetic inputs of the benchmark distributions, `copies` distinct weight buffers to rotate over."""
+    """One GEMM with synthetic inputs of the benchmark distributions, `copies` distinct weight buffers to rotate over.
+    packed: the weights go through afb_prepack first (offline step, outside any timed region)."""
 
-    def __init__(self, lib, torch, m, n, k, *, bits=8, group=0, seed=0, copies=1, variant=0, lda=None, c_f32=False, a=None):
+    def __init__(self, lib, torch, m, n, k, *, bits=8, group=0, seed=0, copies=1, variant=0, lda=None, c_f32=False, a=None, packed=False, flags=0):
         import awesome_fusion_b200 as pkg
         self.lib, self.m, self.n, self.k, self.bits, self.group = lib, m, n, k, bits, group
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -138,10 +139,15 @@ class Gemm:
                 s = (torch.rand((n, k // group), generator=g, device=dev) * 0.045 + 0.005).to(torch.bfloat16)
             else:
                 s = torch.rand((n,), generator=g, device=dev) * 0.009 + 0.001
+            layout = pkg.LAYOUT_COL
+            if packed:
+                lib.prepack(lib.make_args(self.c, self.a, b, s, m, n, k, bits=bits), b, k)   # in place
+                layout = pkg.LAYOUT_COL_PACKED
             self.b.append(b); self.s.append(s)
-            self.args.append(lib.make_args(self.c, self.a, b, s, m, n, k, lda=lda or self.a.stride(0), bits=bits, group=group,
+            self.args.append(lib.make_args(self.c, self.a, b, s, m, n, k, lda=lda or self.a.stride(0), bits=bits, group=group, layout=layout,
                                            scale_dtype=pkg.SCALE_BF16 if group else pkg.SCALE_F32, variant=variant,
-                                           flags=pkg.FLAG_C_F32 if c_f32 else 0))
+                                           flags=flags | (pkg.FLAG_C_F32 if c_f32 else 0)))
+        torch.cuda.synchronize()
         self.flops = gemm_flops(m, n, k)
         self.bytes = gemm_bytes(m, n, k, bits, group)
         self.i = 0
@@ -165,29 +171,51 @@ def time_launches(torch, fn, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
+def time_decode_graph(lib, torch, op, copies, steps, warmup):
+    """A decode launch lasts a few microseconds, less than the host needs to issue it: one CUDA graph holds one launch per
+    rotated weight buffer, so that the events time the device and not the launch loop.  Returns ms per launch."""
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(max(3, warmup)):
+        op.launch(stream)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        cs = torch.cuda.current_stream().cuda_stream
+        for _ in range(copies):
+            op.launch(cs)
+    ms = time_launches(torch, graph.replay, steps, warmup) / copies
+    del graph
+    return ms
+
+
 def single_case(lib, torch, name, m, n, k, bits, group, peaks, steps, warmup):
-    """One single-GPU configuration: kernel-only timing with the weights rotated over more than L2's worth of buffers."""
+    """One single-GPU configuration: kernel-only timing with the weights rotated over more than L2's worth of buffers.
+    Decode shapes are timed three ways, all through afb_gemm_launch: the weights as given; the same with AFB_FLAG_PDL (the
+    launches of the graph overlap: each kernel streams its weights while its predecessor finishes -- legal because weights are
+    constants); and with the weights pre-packed by afb_prepack as well.  The case's own figures are those of the last mode."""
+    import awesome_fusion_b200 as pkg
     stream = torch.cuda.current_stream().cuda_stream
     wbytes = n * k * bits // 8
     copies = max(1, min(24, -(-400_000_000 // wbytes)))   # >= 400 MB of distinct weights (L2 is 126 MB)
     op = Gemm(lib, torch, m, n, k, bits=bits, group=group, seed=1, copies=copies)
-    import awesome_fusion_b200 as pkg
     variant = {pkg.VARIANT_DECODE: "decode", pkg.VARIANT_PREFILL: "prefill", pkg.VARIANT_NAIVE: "naive"}[lib.resolve_variant(op.args[0])]
     timing = "events around back-to-back launches"
+    modes = None
     if variant == "decode" and not os.environ.get("AFB_BENCH_NO_GRAPH"):
-        # a decode launch lasts a few microseconds, less than the host needs to issue it: one CUDA graph holds one launch per
-        # rotated weight buffer, so that the events time the device and not the launch loop
-        for _ in range(max(3, warmup)):
-            op.launch(stream)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            cs = torch.cuda.current_stream().cuda_stream
-            for _ in range(copies):
-                op.launch(cs)
-        ms = time_launches(torch, graph.replay, steps, warmup) / copies
         timing = f"CUDA-graph replay, {copies} launches per graph"
-        del graph
+        modes = {"weights as given": time_decode_graph(lib, torch, op, copies, steps, warmup) * 1e3}
+        for label, packed in (("programmatic dependent launch", False), ("pre-packed weights + programmatic dependent launch", True)):
+            del op
+            torch.cuda.empty_cache()
+            op = Gemm(lib, torch, m, n, k, bits=bits, group=group, seed=1, copies=copies, packed=packed, flags=pkg.FLAG_PDL)
+            try:
+                modes[label] = time_decode_graph(lib, torch, op, copies, steps, warmup) * 1e3
+            except Exception as e:  # noqa: BLE001  (a driver that cannot capture programmatic edges)
+                modes[label] = None
+                timing += f"; {label}: not captured ({type(e).__name__})"
+        best = [v for v in modes.values() if v]
+        ms = (modes["pre-packed weights + programmatic dependent launch"] or min(best)) / 1e3
+        modes = {k_: (round(v, 2) if v else None) for k_, v in modes.items()}
     else:
         ms = time_launches(torch, lambda: op.launch(stream), steps, warmup)
     tf, gb = op.flops / ms / 1e9, op.bytes / ms / 1e6
@@ -197,6 +225,8 @@ def single_case(lib, torch, name, m, n, k, bits, group, peaks, steps, warmup):
            "tflops": round(tf, 2), "gbs": round(gb, 1), "bound": bound, "weight_buffers_rotated": copies, "timing": timing,
            "frac_of_measured": round(gb / peaks["hbm_gbs"] if bound == "hbm" else tf / peaks["bf16_tflops"], 4),
            "frac_of_nominal": round(gb / NOMINAL["hbm_gbs"] if bound == "hbm" else tf / NOMINAL["bf16_tflops"], 4)}
+    if modes:
+        res["us_by_mode"] = modes
     del op
     torch.cuda.empty_cache()
     return res
@@ -205,6 +235,7 @@ def single_case(lib, torch, name, m, n, k, bits, group, peaks, steps, warmup):
 SINGLE_CASES = {
     "decode-m1": (1, 4096, 4096, 8, 0), "decode-m4": (4, 4096, 4096, 8, 0), "decode-m16": (16, 4096, 4096, 8, 0),
     "prefill": (2048, 11008, 4096, 8, 0),
+    "int8-m1": (1, 28672, 8192, 8, 0), "int8-m16": (16, 28672, 8192, 8, 0),
     "int4-m1": (1, 28672, 8192, 4, 128), "int4-m16": (16, 28672, 8192, 4, 128), "int4-m128": (128, 28672, 8192, 4, 128),
     "int4-m4096": (4096, 28672, 8192, 4, 128),
     "cpu-checkable": (256, 1024, 1024, 8, 0),
@@ -415,7 +446,7 @@ def run_ours(args):
     if world == 1:
         cases = []
         if not args.no_cases:
-            for name in ("decode-m1", "decode-m4", "decode-m16", "prefill", "int4-m1", "int4-m16", "int4-m128", "int4-m4096"):
+            for name in ("decode-m1", "decode-m4", "decode-m16", "int8-m1", "int8-m16", "prefill", "int4-m1", "int4-m16", "int4-m128", "int4-m4096"):
                 m, n, k, bits, group = SINGLE_CASES[name]
                 cases.append(single_case(lib, torch, name, m, n, k, bits, group, peaks, 50 if m <= 128 else 10, 5))
             line["cases"] = cases

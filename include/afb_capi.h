@@ -86,6 +86,11 @@ typedef struct afb_gemm_args {
     uint32_t variant;     /* AFB_VARIANT_*                                               */
     uint32_t flags;       /* AFB_FLAG_*                                                  */
     uint32_t reserved;    /* must be 0                                                   */
+    void*    ptr_zero;    /* optional zero-points (NULL = symmetric quantisation): one BYTE per scale entry, same shape as the scales
+                             ([N] or [N][K/group_size], n-major), in the weights' own encoding (int8: like a stored byte; int4: like a
+                             stored nibble, in the low 4 bits).  The weight value is decode(stored) - decode(zero): the reference's fixed
+                             "stored - 128" (bf16gemm_kernel_gfx90a.s:210, mem_transfer.hpp:30) made a per-channel / per-group quantity */
+    uint64_t reserved2;   /* must be 0                                                   */
 } afb_gemm_args;
 
 /* ---- device / memory / events: one per HIP call of the reference driver --------- */
@@ -124,9 +129,10 @@ int afb_device_sync(void);
  * `stream` (NULL = the default stream).  Pointers are DEVICE pointers.
  * GEMMs that split K between CTAs (decode K-slices, short last wave of prefill tiles) meet in an
  * fp32 workspace that belongs to the STREAM they are launched on: launches on one stream are
- * serialised by the stream, launches on different streams use different workspaces.  A stream's
- * workspace (32 MiB) is allocated on its first such launch, which therefore must not happen inside
- * a stream capture; at most 16 streams per device, after that AFB_ERR_TOO_LARGE.            */
+ * serialised by the stream, launches on different streams use different workspaces (32 MiB each).
+ * afb_init allocates four of them; a fifth and later stream allocates its own on its first such
+ * launch, which then must not happen inside a stream capture; at most 16 streams per device, after
+ * that AFB_ERR_TOO_LARGE.  A captured graph keeps using the workspace of the stream it was captured on. */
 int afb_gemm_launch(const afb_gemm_args* args, void* stream);
 /* Which variant AFB_VARIANT_AUTO resolves to for these args (no launch). */
 int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
@@ -157,6 +163,32 @@ int afb_gemm_launch_static(const afb_gemm_args* args, void* stream);
  * ldb = out_ldb; its result is bit-identical to the GEMM on the plain [N,K] weights.  [N,K] input may be packed
  * in place (out_b == ptr_b, out_ldb == ldb).  Asynchronous on `stream`. */
 int afb_prepack(const afb_gemm_args* args, void* out_b, uint32_t out_ldb, void* stream);
+/* ---- fused neighbours of the GEMM ------------------------------------------------ */
+/* The reference's stated purpose is "gemm fusion for llm" (README.md:2); its kernel fuses dequantisation into the GEMM
+ * (bf16gemm_kernel_gfx90a.s:410-489).  These entry points fuse what stands on the other side of it in a gated MLP:
+ *     v[m,r]  = (A x dequant(B)^T)[m,r] + bias[r]                        r = row of B, bias optional
+ *     plain:    C[m,r] = act(v[m,r]) + residual[m,r]
+ *     gated:    C[m,i] = act(v[m,2i]) * v[m,2i+1] + residual[m,i]          rows 2i / 2i+1 of B = gate / up projection of channel i
+ * all in fp32 from the fp32 accumulator, rounded to bf16 once.  gemm.n counts the rows of B (twice the output channels when
+ * gated), gemm.ptr_c / gemm.ldc describe the bf16 result [M, N_out].  B in [N,K] layout, plain or pre-packed.            */
+#define AFB_ACT_NONE 0u
+#define AFB_ACT_SILU 1u   /* x / (1 + exp(-x)) */
+typedef struct afb_fused_args {
+    afb_gemm_args gemm;
+    uint32_t gated;          /* 0 / 1 */
+    uint32_t activation;     /* AFB_ACT_* */
+    void*    ptr_bias;       /* optional fp32 [gemm.n] */
+    void*    ptr_residual;   /* optional bf16 [M, N_out] */
+    uint32_t ld_residual;    /* elements */
+    uint32_t reserved;       /* must be 0 */
+} afb_fused_args;
+int afb_gemm_fused_launch(const afb_fused_args* args, void* stream);
+/* Builds the B of a gated launch from two separate projections of equal shape and format ([N,K] plain layout): row 2i of the
+ * output is row i of the gate projection, row 2i+1 row i of the up projection, in the pre-packed word order (AFB_LAYOUT_COL_PACKED,
+ * pitch out_ldb elements); scales (and zero-points, when gate->ptr_zero is set) are interleaved the same way into out_scale
+ * (and out_zero).  gate->n is N, the output has 2N rows.  Asynchronous on `stream`. */
+int afb_prepack_gated(const afb_gemm_args* gate, const void* b_up, const void* scale_up, const void* zero_up, void* out_b,
+                      uint32_t out_ldb, void* out_scale, void* out_zero, void* stream);
 /* Dequantised weights exactly as the kernels feed them to the tensor cores:
  * out is bf16 with B's logical shape and layout ([N,K] ld=K for COL, [K,N] ld=N for ROW).
  * group_size == 0: the exact integer value; else bf16_rn(float(q) * float(scale)).
@@ -223,9 +255,9 @@ int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* args, void* 
  * LOCAL slots (partial[q] = own_stage + (q * (M/world) - rank * (M/world)) * N floats, ld_partial = N): its first phase then
  * waits for every rank's GEMM, its sum reads local memory only, and its second phase broadcasts the bf16 rows. */
 int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream);
-/* sizeof(afb_gemm_args), sizeof(afb_allreduce_args), sizeof(afb_tile_allreduce_args) as this library was compiled: a binding
- * in another language compares them with its own declarations before the first call.  Needs no GPU. */
-int afb_abi_sizes(uint32_t sizes[3]);
+/* sizeof(afb_gemm_args), sizeof(afb_allreduce_args), sizeof(afb_tile_allreduce_args), sizeof(afb_fused_args) as this library was
+ * compiled: a binding in another language compares them with its own declarations before the first call.  Needs no GPU. */
+int afb_abi_sizes(uint32_t sizes[4]);
 /* fp32 [rows, cols] (ld_src) -> bf16 (ld_dst), round to nearest even: finishes a K-split whose partial
  * sums were combined by a library collective instead of afb_ksplit_allreduce_launch. */
 int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uint32_t cols, uint32_t ld_dst, uint32_t ld_src, void* stream);

@@ -52,6 +52,7 @@ inline uint16_t f32_to_bf16_rne(float f) {  // datatype.hpp:80-121
 struct Args {
     uint32_t m, n, k, lda, ldb, ldc;
     uint32_t bits, enc, layout, scale_dtype, group;
+    const uint8_t* zero = nullptr;   // optional zero-points: one byte per scale entry, in the weights' encoding
 };
 
 // Position of weight k inside its 32-bit word in the pre-packed [N,K] layout (layout 2): the GPU kernels' cheap unpack
@@ -63,17 +64,25 @@ inline uint32_t packed_pos(uint32_t bits, uint32_t k) {
     return (k & ~7u) | ((i >> 1) | ((i & 1u) << 2));
 }
 
+inline int decode8(uint8_t u, uint32_t enc) { return enc == 1 ? (int)u - 128 : (int)(int8_t)u; }
+inline int decode4(int nib, uint32_t enc) { return enc == 1 ? nib - 8 : (nib >= 8 ? nib - 16 : nib); }
 // Integer value of weight (n, k), exact.  layout 0: [K,N]; 1: [N,K]; 2: [N,K] pre-packed.
+// With zero-points the value is decode(stored) - decode(zero): the fixed "stored - 128" of the reference
+// (mem_transfer.hpp:30, bf16gemm_kernel_gfx90a.s:210) with the 128 replaced by a per-channel / per-group byte.
 inline int weight_q(const uint8_t* b, const Args& a, uint32_t n, uint32_t k) {
     const uint32_t kk = a.layout == 2 ? packed_pos(a.bits, k) : k;
+    int z = 0;
+    if (a.zero) {
+        const uint8_t zb = a.zero[a.group ? (size_t)n * (a.k / a.group) + k / a.group : n];
+        z = a.bits == 8 ? decode8(zb, a.enc) : decode4(zb & 0xF, a.enc);
+    }
     if (a.bits == 8) {
         const size_t idx = a.layout != 0 ? (size_t)n * a.ldb + kk : (size_t)k * a.ldb + n;
-        const uint8_t u = b[idx];
-        return a.enc == 1 ? (int)u - 128 : (int)(int8_t)u;
+        return decode8(b[idx], a.enc) - z;
     }
     const uint8_t byte = b[(size_t)n * (a.ldb / 2) + kk / 2];
     const int nib = (kk & 1) ? (byte >> 4) : (byte & 0xF);
-    return a.enc == 1 ? nib - 8 : (nib >= 8 ? nib - 16 : nib);
+    return decode4(nib, a.enc) - z;
 }
 inline float scale_at(const void* s, const Args& a, uint32_t n, uint32_t k) {
     const size_t idx = a.group ? (size_t)n * (a.k / a.group) + k / a.group : n;
@@ -129,8 +138,8 @@ void afb_oracle_f32_to_i4(const float* src, uint8_t* dst, size_t n, uint32_t enc
 // Dequantised weights as bf16 in B's own logical shape ([N,K] ld=K for layout 1, [K,N] ld=N for layout 0):
 // group == 0: the exact integer; else bf16_rne(float(q) * float(scale)).
 void afb_oracle_dequant_bf16(uint16_t* out, const uint8_t* b, const void* scale, uint32_t n, uint32_t k, uint32_t ldb,
-                             uint32_t bits, uint32_t enc, uint32_t layout, uint32_t scale_dtype, uint32_t group) {
-    Args a{0, n, k, 0, ldb, 0, bits, enc, layout, scale_dtype, group};
+                             uint32_t bits, uint32_t enc, uint32_t layout, uint32_t scale_dtype, uint32_t group, const uint8_t* zero) {
+    Args a{0, n, k, 0, ldb, 0, bits, enc, layout, scale_dtype, group, zero};
     for (uint32_t in = 0; in < n; ++in)
         for (uint32_t ik = 0; ik < k; ++ik) {
             float w = (float)weight_q(b, a, in, ik);
@@ -161,8 +170,8 @@ void afb_oracle_prepack(uint8_t* out, const uint8_t* b, uint32_t n, uint32_t k, 
 // otherwise rows of C are split over `threads` host threads, each element computed identically.
 void afb_oracle_gemm(float* c, const uint16_t* a_bf16, const uint8_t* b, const void* scale, uint32_t m, uint32_t n,
                      uint32_t k, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t bits, uint32_t enc, uint32_t layout,
-                     uint32_t scale_dtype, uint32_t group, int round_w, int threads) {
-    Args a{m, n, k, lda, ldb, ldc, bits, enc, layout, scale_dtype, group};
+                     uint32_t scale_dtype, uint32_t group, int round_w, int threads, const uint8_t* zero) {
+    Args a{m, n, k, lda, ldb, ldc, bits, enc, layout, scale_dtype, group, zero};
     if (threads <= 1) { gemm_rows(c, a_bf16, b, scale, a, 0, m, round_w); return; }
     if ((uint32_t)threads > m) threads = (int)m;
     std::vector<std::thread> pool;

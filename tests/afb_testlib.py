@@ -28,8 +28,8 @@ class Oracle:
         L.afb_oracle_bf16_to_f32.argtypes = [_u16p, _f32p, sz]
         L.afb_oracle_f32_to_i8.argtypes = [_f32p, _u8p, sz, u32]
         L.afb_oracle_f32_to_i4.argtypes = [_f32p, _u8p, sz, u32]
-        L.afb_oracle_dequant_bf16.argtypes = [_u16p, _u8p, vp, u32, u32, u32, u32, u32, u32, u32, u32]
-        L.afb_oracle_gemm.argtypes = [_f32p, _u16p, _u8p, vp] + [u32] * 11 + [i, i]
+        L.afb_oracle_dequant_bf16.argtypes = [_u16p, _u8p, vp, u32, u32, u32, u32, u32, u32, u32, u32, vp]
+        L.afb_oracle_gemm.argtypes = [_f32p, _u16p, _u8p, vp] + [u32] * 11 + [i, i, vp]
         L.afb_oracle_prepack.argtypes = [_u8p, _u8p] + [u32] * 6
         L.afb_oracle_gemm_rrr.argtypes = [_f32p, _f32p, _f32p, _f32p] + [sz] * 6
         L.afb_oracle_compare.argtypes = [_f32p, _u16p, sz, ctypes.c_float, ctypes.POINTER(ctypes.c_double),
@@ -71,8 +71,13 @@ class Oracle:
         shape = (c.n, c.k) if c.layout != 0 else (c.k, c.n)
         out = np.empty(shape, np.uint16)
         self.lib.afb_oracle_dequant_bf16(_p(out, _u16p), _p(c.b, _u8p), c.scale.ctypes.data, c.n, c.k, c.ldb, c.bits, c.enc,
-                                         c.layout, c.scale_dtype, c.group)
+                                         c.layout, c.scale_dtype, c.group, self._zero_ptr(c))
         return out
+
+    @staticmethod
+    def _zero_ptr(case):
+        z = getattr(case, "zero", None)
+        return None if z is None else z.ctypes.data
 
     def prepack(self, case, out_ldb=None):
         """The Case with B pre-packed (layout 2), by the CPU restatement of afb_prepack."""
@@ -89,7 +94,7 @@ class Oracle:
         m = a.shape[0]
         out = np.empty((m, c.n), np.float32)
         self.lib.afb_oracle_gemm(_p(out, _f32p), _p(a, _u16p), _p(c.b, _u8p), c.scale.ctypes.data, m, c.n, c.k, c.k, c.ldb,
-                                 c.n, c.bits, c.enc, c.layout, c.scale_dtype, c.group, int(round_w), threads)
+                                 c.n, c.bits, c.enc, c.layout, c.scale_dtype, c.group, int(round_w), threads, self._zero_ptr(c))
         return out
 
     def gemm_rrr(self, a, b, scale):
@@ -181,7 +186,7 @@ class Case:
 
 
 def make_case(m, n, k, *, bits=8, group=0, layout=1, enc=0, scale_dtype=None, seed=0, a_dist="normal",
-              scale_range=(0.001, 0.01), integer_data=False, qmax=None):
+              scale_range=(0.001, 0.01), integer_data=False, qmax=None, zero_points=False):
     """Seeded inputs with the distributions the benchmark configurations name: A ~ N(0,1) (or
     uniform[-1,1]) rounded to bf16; B integers uniform in [-127,127] (int8) or [-8,7] (int4);
     scales uniform in ``scale_range``.  ``integer_data`` reproduces the reference's own test data
@@ -215,8 +220,13 @@ def make_case(m, n, k, *, bits=8, group=0, layout=1, enc=0, scale_dtype=None, se
         u = (q.view(np.uint8) ^ np.uint8(0x8 if enc == 1 else 0)) & np.uint8(0xF)
         b = u[:, 0::2] | (u[:, 1::2] << np.uint8(4))
         ldb = k
+    zero = None
+    if zero_points:   # one byte per scale entry, in the weights' own encoding: any int8 value / any nibble
+        zv = rng.integers(-128, 128, size=(n, ngroups)) if bits == 8 else rng.integers(-8, 8, size=(n, ngroups))
+        zero = (zv.astype(np.int8).view(np.uint8) ^ np.uint8((0x80 if bits == 8 else 0x8) if enc == 1 else 0)) & np.uint8(0xFF if bits == 8 else 0xF)
+        zero = np.ascontiguousarray(zero.reshape(n, ngroups) if group else zero.reshape(n))
     return Case(m=m, n=n, k=k, bits=bits, group=group, layout=layout, enc=enc, scale_dtype=scale_dtype, a=a, b=np.ascontiguousarray(b),
-                scale=np.ascontiguousarray(scale), q=q, ldb=ldb, seed=seed)
+                scale=np.ascontiguousarray(scale), q=q, ldb=ldb, seed=seed, zero=zero)
 
 
 # --------------------------------------------------------------------------------------
@@ -242,6 +252,7 @@ class DeviceCase:
         self.d_a = lib.to_device(a_host)
         self.d_b = lib.to_device(b_host)
         self.d_s = lib.to_device(case.scale)
+        self.d_z = lib.to_device(case.zero) if getattr(case, "zero", None) is not None else None
         self.d_c_base = lib.malloc(self.c_bytes + 2 * guard)
         lib.memset(self.d_c_base, 0xCD, self.c_bytes + 2 * guard)
         self.d_c = self.d_c_base + guard
@@ -250,7 +261,7 @@ class DeviceCase:
         c = self.case
         return self.lib.make_args(self.d_c, self.d_a, self.d_b, self.d_s, c.m, c.n, c.k, lda=self.lda, ldb=self.ldb, ldc=self.ldc, bits=c.bits,
                                   encoding=c.enc, layout=c.layout, scale_dtype=c.scale_dtype, group=c.group, variant=variant,
-                                  flags=flags)
+                                  flags=flags, zero=self.d_z)
 
     def result(self):
         """C as a [M, N] array (bf16 bits or fp32) and the raw buffer including guards."""
@@ -264,8 +275,9 @@ class DeviceCase:
         return full[:, :c.n].copy(), raw
 
     def close(self):
-        for p in (self.d_a, self.d_b, self.d_s, self.d_c_base):
-            self.lib.free(p)
+        for p in (self.d_a, self.d_b, self.d_s, self.d_c_base, self.d_z):
+            if p is not None:
+                self.lib.free(p)
 
 
 def run_case(lib, case, variant=0, c_f32=False, ldc=None, guard=0, flags=0, lda=None, ldb=None):

@@ -85,11 +85,11 @@ def test_push_staging_layout_matches_exchange_addressing():
 
 
 def test_struct_layouts_match_the_library():
-    """The ctypes mirrors of the three argument blocks have the sizes the library was compiled with (no GPU needed)."""
+    """The ctypes mirrors of the four argument blocks have the sizes the library was compiled with (no GPU needed)."""
     import ctypes
     import awesome_fusion_b200 as pkg
     from awesome_fusion_b200 import dist as D
     lib = pkg.load()
-    sizes = (ctypes.c_uint32 * 3)()
+    sizes = (ctypes.c_uint32 * 4)()
     assert lib.lib.afb_abi_sizes(sizes) == 0
-    assert list(sizes) == [ctypes.sizeof(pkg.GemmArgs), ctypes.sizeof(D.AllReduceArgs), ctypes.sizeof(D.TileAllReduceArgs)]
+    assert list(sizes) == [ctypes.sizeof(pkg.GemmArgs), ctypes.sizeof(D.AllReduceArgs), ctypes.sizeof(D.TileAllReduceArgs), ctypes.sizeof(pkg.FusedArgs)]

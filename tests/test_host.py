@@ -35,7 +35,7 @@ def test_args_struct_layout_matches_reference_block():
     A = pkg.GemmArgs
     assert [A.ptr_c.offset, A.ptr_a.offset, A.ptr_b.offset, A.ptr_scale.offset] == [0, 8, 16, 24]
     assert [A.m.offset, A.n.offset, A.k.offset, A.lda.offset, A.ldb.offset, A.ldc.offset] == [32, 36, 40, 44, 48, 52]
-    assert ctypes.sizeof(A) == 88
+    assert ctypes.sizeof(A) == 104 and A.ptr_zero.offset == 88
 
 
 def test_validation_without_gpu(lib):
