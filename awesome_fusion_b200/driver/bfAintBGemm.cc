@@ -14,6 +14,11 @@
 //   a_dist=normal|uniform   real data: A ~ N(0,1) (default) or uniform[-1,1]
 //   scale_lo=X scale_hi=Y   real data: range of the scales (defaults 0.001..0.01 per channel, 0.005..0.05 per group)
 //   exact=0|1          group scales, prefill variant: two bf16 terms per weight (AFB_FLAG_GROUP_EXACT) instead of one rounded term
+//   prepack=0|1        run afb_prepack on B first (outside the timed loop) and multiply the pre-packed weights: this is how
+//                      the reference's own [K,N] layout (b_layout=row) reaches the fast kernels
+//   gpus=G split=n|k   shard the GEMM over G GPUs of the box from this one process (afb_dist_*): n = output channels
+//                      (column-parallel, no collective), k = the K dimension (row-parallel, partial sums added over NVLink);
+//                      needs b_layout=col, bits=8, group=0
 //   seed=S  iters=I  warmup=W  variant=auto|decode|prefill|naive
 #include <cmath>
 #include <cstdint>
@@ -45,7 +50,8 @@ namespace {
 constexpr float kGroupedOneTermBound = 0.25f;   // group-scaled prefill, one rounded term per weight, against the fp32 formula at the 0.05 x RMS floor
 struct Options {
     int validation = 0, m = 32, n = 128, k = 512, lda = -1, ldb = -1, ldc = -1;
-    bool b_col = false, offset_enc = true, real_data = false, a_uniform = false, exact = false;
+    bool b_col = false, offset_enc = true, real_data = false, a_uniform = false, exact = false, prepack = false, split_k = false;
+    int gpus = 1;
     float scale_lo = -1.f, scale_hi = -1.f;
     int bits = 8, group = 0, iters = 10, warmup = 10;
     unsigned long long seed = 0;
@@ -67,6 +73,9 @@ bool parse(int argc, char** argv, Options& o) {
         else if (key == "scale_lo") o.scale_lo = (float)std::atof(val.c_str());
         else if (key == "scale_hi") o.scale_hi = (float)std::atof(val.c_str());
         else if (key == "exact") o.exact = std::atoi(val.c_str()) != 0;
+        else if (key == "prepack") o.prepack = std::atoi(val.c_str()) != 0;
+        else if (key == "gpus") o.gpus = std::atoi(val.c_str());
+        else if (key == "split") o.split_k = val == "k";
         else if (key == "seed") o.seed = std::strtoull(val.c_str(), nullptr, 10);
         else if (key == "iters") o.iters = std::atoi(val.c_str());
         else if (key == "warmup") o.warmup = std::atoi(val.c_str());
@@ -79,7 +88,109 @@ bool parse(int argc, char** argv, Options& o) {
     if (pos.size() >= 7) { o.lda = std::atoi(pos[4]); o.ldb = std::atoi(pos[5]); o.ldc = std::atoi(pos[6]); }
     if (o.bits == 4 && !o.b_col) { std::printf("bits=4 needs b_layout=col\n"); return false; }
     if (o.m <= 0 || o.n <= 0 || o.k <= 0 || o.iters <= 0) return false;
+    if (o.gpus < 1 || o.gpus > AFB_MAX_RANKS) { std::printf("gpus must be 1..%d\n", AFB_MAX_RANKS); return false; }
+    if (o.gpus > 1 && (!o.b_col || o.bits != 8 || o.group != 0 || o.lda != o.k || o.ldb != o.k || o.ldc != o.n)) {
+        std::printf("gpus=G needs b_layout=col, bits=8, group=0 and default leading dimensions\n");
+        return false;
+    }
     return true;
+}
+
+// The sharded run: the same timing loop and metric line, with the GEMM cut over o.gpus GPUs by afb_dist_*.
+// a_dev / b_dev / s_host are the device-format host copies (bf16 A [M,K], int8 B [N,K], fp32 scales [N]); ref_inputs are the
+// fp32 masters the check multiplies.  Returns the process exit code.
+int run_sharded(const Options& o, const void* a_dev, const void* b_dev, const float* s_host, const float* a_f32, const float* b_f32) {
+    const int m = o.m, n = o.n, k = o.k, world = o.gpus;
+    afb_dist* dist = nullptr;
+    GPU_CHECK_ERROR(afb_dist_init((uint32_t)world, &dist));
+    struct Rank { void *a = nullptr, *b = nullptr, *s = nullptr, *c = nullptr; uint32_t lo = 0, hi = 0; void *ev0 = nullptr, *ev1 = nullptr, *stream = nullptr; };
+    std::vector<Rank> rk(world);
+    afb_dist_gemm_args da = {};
+    da.split = o.split_k ? AFB_SPLIT_K : AFB_SPLIT_N;
+    for (int r = 0; r < world; ++r) {
+        GPU_CHECK_ERROR(afb_init(r));   // also makes device r current for the allocations below
+        GPU_CHECK_ERROR(afb_dist_split_range(o.split_k ? k : n, world, r, o.split_k ? 64 : 8, &rk[r].lo, &rk[r].hi));
+        // every GPU gets the whole A; B and the scales are cut (N-split) or addressed with an offset and the full pitch (K-split)
+        GPU_CHECK_ERROR(afb_malloc(&rk[r].a, (std::size_t)m * k * 2));
+        GPU_CHECK_ERROR(afb_memcpy_h2d(rk[r].a, a_dev, (std::size_t)m * k * 2));
+        const std::size_t b_rows = o.split_k ? n : rk[r].hi - rk[r].lo, b_row0 = o.split_k ? 0 : rk[r].lo;
+        GPU_CHECK_ERROR(afb_malloc(&rk[r].b, b_rows * k));
+        GPU_CHECK_ERROR(afb_memcpy_h2d(rk[r].b, static_cast<const char*>(b_dev) + b_row0 * k, b_rows * k));
+        GPU_CHECK_ERROR(afb_malloc(&rk[r].s, b_rows * 4));
+        GPU_CHECK_ERROR(afb_memcpy_h2d(rk[r].s, s_host + b_row0, b_rows * 4));
+        const std::size_t c_cols = o.split_k ? n : rk[r].hi - rk[r].lo;
+        GPU_CHECK_ERROR(afb_malloc(&rk[r].c, (std::size_t)m * c_cols * 2));
+        GPU_CHECK_ERROR(afb_memset(rk[r].c, 0, (std::size_t)m * c_cols * 2));
+        afb_gemm_args& g = da.shard[r];
+        g.ptr_c = rk[r].c; g.ptr_scale = rk[r].s;
+        g.m = m;
+        g.b_bits = 8; g.b_encoding = o.offset_enc ? AFB_ENC_OFFSET_BINARY : AFB_ENC_TWOS_COMPLEMENT; g.b_layout = AFB_LAYOUT_COL;
+        g.scale_dtype = AFB_SCALE_F32; g.variant = o.variant;
+        if (o.split_k) {
+            g.ptr_a = static_cast<char*>(rk[r].a) + (std::size_t)rk[r].lo * 2; g.ptr_b = static_cast<char*>(rk[r].b) + rk[r].lo;
+            g.n = n; g.k = rk[r].hi - rk[r].lo; g.lda = k; g.ldb = k; g.ldc = n;
+            da.c[r] = rk[r].c;
+        } else {
+            g.ptr_a = rk[r].a; g.ptr_b = rk[r].b;
+            g.n = rk[r].hi - rk[r].lo; g.k = k; g.lda = k; g.ldb = k; g.ldc = g.n;
+        }
+        GPU_CHECK_ERROR(afb_dist_stream(dist, r, &rk[r].stream));
+        GPU_CHECK_ERROR(afb_event_create(&rk[r].ev0));
+        GPU_CHECK_ERROR(afb_event_create(&rk[r].ev1));
+    }
+    for (int i = 0; i < o.warmup; ++i) GPU_CHECK_ERROR(afb_dist_gemm_launch(dist, &da));
+    GPU_CHECK_ERROR(afb_dist_sync(dist));
+    for (int r = 0; r < world; ++r) { GPU_CHECK_ERROR(afb_init(r)); GPU_CHECK_ERROR(afb_event_record(rk[r].ev0, rk[r].stream)); }
+    for (int i = 0; i < o.iters; ++i) GPU_CHECK_ERROR(afb_dist_gemm_launch(dist, &da));
+    for (int r = 0; r < world; ++r) { GPU_CHECK_ERROR(afb_init(r)); GPU_CHECK_ERROR(afb_event_record(rk[r].ev1, rk[r].stream)); }
+    GPU_CHECK_ERROR(afb_dist_sync(dist));
+    float elapsed_ms = 0.f;   // the slowest GPU decides
+    for (int r = 0; r < world; ++r) {
+        float ms = 0.f;
+        GPU_CHECK_ERROR(afb_init(r));
+        GPU_CHECK_ERROR(afb_event_elapsed_ms(&ms, rk[r].ev0, rk[r].ev1));
+        if (ms > elapsed_ms) elapsed_ms = ms;
+        int32_t status[4] = {0, 0, 0, 0};
+        GPU_CHECK_ERROR(afb_read_status(status));
+        if (status[0] != 0) { std::printf("device %d status %d (%s) at %d/%d/%d\n", r, status[0], afb_status_string(status[0]), status[1], status[2], status[3]); return 1; }
+    }
+    const double time_per_loop = elapsed_ms / o.iters, flops = 2.0 * m * n * k;
+    const double bytes = 2.0 * ((double)m * k + (double)m * n) + (double)n * k + 4.0 * n;
+    std::printf("m: %d, n: %d, k: %d, time: %.3f ms, tflops: %.3f, bw: %.3f GB/s, variant: sharded over %d GPUs (%s-split)\n", m, n, k, time_per_loop,
+                flops / time_per_loop / 1e9, bytes / time_per_loop / 1e6, world, o.split_k ? "k" : "n");
+    std::printf("\n");
+    int rc = 0;
+    if (o.validation) {
+        std::vector<float> ref((std::size_t)m * n);
+        gemm_ref(ref.data(), a_f32, b_f32, s_host, m, n, k, k, k, n, true, 0);
+        std::vector<CDataType> got((std::size_t)m * n), part;
+        const float nrms = o.real_data ? 5e-3f : 2e-3f, rel = o.real_data ? 1e-2f : 4e-3f;
+        bool res = true;
+        if (o.split_k) {   // every GPU holds the complete result: check them all
+            for (int r = 0; r < world && res; ++r) {
+                GPU_CHECK_ERROR(afb_init(r));
+                GPU_CHECK_ERROR(afb_memcpy_d2h(got.data(), rk[r].c, got.size() * 2));
+                res = valid_vector<CDataType>(ref.data(), got.data(), m * n, nrms, rel, 0.05f);
+            }
+        } else {           // the channel shards side by side
+            for (int r = 0; r < world; ++r) {
+                const std::size_t cols = rk[r].hi - rk[r].lo;
+                part.resize((std::size_t)m * cols);
+                GPU_CHECK_ERROR(afb_init(r));
+                GPU_CHECK_ERROR(afb_memcpy_d2h(part.data(), rk[r].c, part.size() * 2));
+                for (int row = 0; row < m; ++row) std::memcpy(&got[(std::size_t)row * n + rk[r].lo], &part[(std::size_t)row * cols], cols * 2);
+            }
+            res = valid_vector<CDataType>(ref.data(), got.data(), m * n, nrms, rel, 0.05f);
+        }
+        std::printf(",%s \n", res ? "valid" : "fail");
+        rc = res ? 0 : 1;
+    }
+    for (int r = 0; r < world; ++r) {
+        (void)afb_event_destroy(rk[r].ev0); (void)afb_event_destroy(rk[r].ev1);
+        (void)afb_free(rk[r].a); (void)afb_free(rk[r].b); (void)afb_free(rk[r].s); (void)afb_free(rk[r].c);
+    }
+    GPU_CHECK_ERROR(afb_dist_finalize(dist));
+    return rc;
 }
 }  // namespace
 
@@ -129,6 +240,11 @@ int main(int argc, char** argv) {
     if (scale_bf16) mem_transfer_bf16_rne(scale_host_buf_to_device, scale_host_buf, s_elems);
     else std::memcpy(scale_host_buf_to_device.GetBuffer(), s_f32, 4 * s_elems);
 
+    if (o.gpus > 1) {
+        if (scale_bf16) { std::printf("gpus=G needs per-channel fp32 scales\n"); return 2; }
+        return run_sharded(o, a_host_buf_to_device.GetBuffer(), b_host_buf_to_device.GetBuffer(), s_f32, a_f32, b_f32);
+    }
+
     SimpleDeviceMem a_device_buf(sizeof(ADataType) * a_elems), b_device_buf(b_bytes), c_device_buf(sizeof(CDataType) * c_elems),
         scale_device_buf((scale_bf16 ? 2 : 4) * s_elems);
     if (!a_device_buf.ok() || !b_device_buf.ok() || !c_device_buf.ok() || !scale_device_buf.ok()) { std::printf("device allocation failed\n"); return 1; }
@@ -151,6 +267,15 @@ int main(int argc, char** argv) {
     args.group_size = o.group;
     args.variant = o.variant;
     args.flags = o.exact ? AFB_FLAG_GROUP_EXACT : 0u;
+    // optional offline step: the weights re-ordered (and, from the reference's [K,N] layout, transposed) for the fast kernels
+    SimpleDeviceMem packed_device_buf(o.prepack ? (std::size_t)n * k * o.bits / 8 : 1);
+    if (o.prepack) {
+        if (!packed_device_buf.ok()) { std::printf("device allocation failed\n"); return 1; }
+        GPU_CHECK_ERROR(afb_prepack(&args, packed_device_buf.GetBuffer(), (uint32_t)k, nullptr));
+        args.ptr_b = packed_device_buf.GetBuffer();
+        args.ldb = k;
+        args.b_layout = AFB_LAYOUT_COL_PACKED;
+    }
     unsigned chosen = 0;
     GPU_CHECK_ERROR(afb_gemm_resolve_variant(&args, &chosen));
 

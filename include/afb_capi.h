@@ -255,6 +255,33 @@ int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* args, void* 
  * LOCAL slots (partial[q] = own_stage + (q * (M/world) - rank * (M/world)) * N floats, ld_partial = N): its first phase then
  * waits for every rank's GEMM, its sum reads local memory only, and its second phase broadcasts the bf16 rows. */
 int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t world, uint32_t rank, void* stream);
+/* ---- the sharded GEMM from ONE process (one host thread, one stream per GPU, peer access instead of IPC) ---------
+ * The multi-GPU extension of the reference driver's single-device set-up (bfAintBGemm.cc:63).  afb_dist_init(ngpus)
+ * initialises devices 0 .. ngpus-1 (afb_init on each), enables peer access between all pairs and creates one stream per
+ * GPU; afb_dist_gemm_launch issues one sharded GEMM on those streams and returns without waiting; afb_dist_sync waits
+ * for all of them.  shard[r] holds DEVICE-r pointers.
+ *   AFB_SPLIT_N  column-parallel: shard[r] is an ordinary GEMM on GPU r's channels, written to its own ptr_c.  No collective.
+ *   AFB_SPLIT_K  row-parallel (int8, per-channel scales): shard[r] multiplies A[:, K_r] by B[:, K_r] (same m and n on every
+ *                rank; shard[r].ptr_c is ignored); the fp32 partial sums are added in rank order over NVLink peer memory and
+ *                every c[r] (bf16 [M,N], ld = N, on GPU r) receives the complete result.  The reduce-scatter runs in the
+ *                GEMM epilogue when M is a multiple of 256 * ngpus, else in the exchange kernel. */
+#define AFB_SPLIT_N 0u
+#define AFB_SPLIT_K 1u
+typedef struct afb_dist afb_dist;
+typedef struct afb_dist_gemm_args {
+    afb_gemm_args shard[AFB_MAX_RANKS];
+    void*    c[AFB_MAX_RANKS];   /* AFB_SPLIT_K only */
+    uint32_t split;              /* AFB_SPLIT_* */
+    uint32_t wait_ms;            /* bound of each cross-GPU wait (0 = 2000) */
+} afb_dist_gemm_args;
+int afb_dist_init(uint32_t ngpus, afb_dist** dist);
+int afb_dist_world(const afb_dist* dist, uint32_t* world);
+int afb_dist_stream(afb_dist* dist, uint32_t rank, void** stream);   /* GPU `rank`'s stream: for events and copies ordered with the GEMMs */
+int afb_dist_gemm_launch(afb_dist* dist, const afb_dist_gemm_args* args);
+int afb_dist_sync(afb_dist* dist);
+int afb_dist_finalize(afb_dist* dist);
+/* [lo, hi) of `total` owned by `rank`: whole units of `multiple`, the remainder to the first ranks.  Needs no GPU. */
+int afb_dist_split_range(uint32_t total, uint32_t world, uint32_t rank, uint32_t multiple, uint32_t* lo, uint32_t* hi);
 /* sizeof(afb_gemm_args), sizeof(afb_allreduce_args), sizeof(afb_tile_allreduce_args), sizeof(afb_fused_args) as this library was
  * compiled: a binding in another language compares them with its own declarations before the first call.  Needs no GPU. */
 int afb_abi_sizes(uint32_t sizes[4]);
