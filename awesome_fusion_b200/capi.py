@@ -31,10 +31,10 @@ EXPORTS = [
     "afb_free_host", "afb_memcpy_h2d", "afb_memcpy_d2h", "afb_memcpy_d2d", "afb_memset", "afb_event_create",
     "afb_event_record", "afb_event_sync", "afb_event_elapsed_ms", "afb_event_destroy", "afb_stream_create",
     "afb_stream_sync", "afb_stream_destroy", "afb_device_sync", "afb_gemm_launch", "afb_gemm_resolve_variant",
-    "afb_gemm_host", "afb_gemm_launch_static", "afb_prepack", "afb_prepack_gated", "afb_gemm_fused_launch", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
+    "afb_gemm_host", "afb_gemm_host_async", "afb_gemm_host_wait", "afb_gemm_launch_static", "afb_prepack", "afb_prepack_gated", "afb_gemm_fused_launch", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
     "afb_ksplit_allreduce_launch", "afb_cast_f32_to_bf16", "afb_ksplit_tile_info", "afb_gemm_launch_tiles", "afb_ksplit_tile_allreduce_launch", "afb_gemm_launch_push", "afb_abi_sizes",
     "afb_dist_init", "afb_dist_world", "afb_dist_stream", "afb_dist_gemm_launch", "afb_dist_sync", "afb_dist_finalize", "afb_dist_split_range",
-    "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
+    "afb_ksplit_sub_info", "afb_gemm_launch_push_pipelined", "afb_ksplit_sub_allreduce_launch", "afb_phase_timestamps", "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
 ]
 
 
@@ -111,6 +111,8 @@ class Library:
         L.afb_gemm_launch.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_gemm_resolve_variant.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(ctypes.c_uint32)]
         L.afb_gemm_host.argtypes = [ctypes.POINTER(GemmArgs), vp]
+        L.afb_gemm_host_async.argtypes = [ctypes.POINTER(GemmArgs), vp]
+        L.afb_gemm_host_wait.argtypes = [vp]
         L.afb_gemm_launch_static.argtypes = [ctypes.POINTER(GemmArgs), vp]
         L.afb_dequant_dump.argtypes = [ctypes.POINTER(GemmArgs), vp, vp]
         L.afb_prepack.argtypes = [ctypes.POINTER(GemmArgs), vp, ctypes.c_uint32, vp]
@@ -259,6 +261,12 @@ class Library:
     def gemm_host(self, args, stream=None):
         self.check(self.lib.afb_gemm_host(ctypes.byref(args), stream), "afb_gemm_host")
 
+    def gemm_host_async(self, args, stream=None):
+        self.check(self.lib.afb_gemm_host_async(ctypes.byref(args), stream), "afb_gemm_host_async")
+
+    def gemm_host_wait(self, stream=None):
+        self.check(self.lib.afb_gemm_host_wait(stream), "afb_gemm_host_wait")
+
     def resolve_variant(self, args):
         v = ctypes.c_uint32(0)
         self.check(self.lib.afb_gemm_resolve_variant(ctypes.byref(args), ctypes.byref(v)), "afb_gemm_resolve_variant")
@@ -293,6 +301,12 @@ class Library:
     def read_status(self):
         out = (ctypes.c_int32 * 4)()
         self.check(self.lib.afb_read_status(out), "afb_read_status")
+        return list(out)
+
+    def phase_timestamps(self):
+        """afb_phase_timestamps: ns stamps of the last row-parallel GEMM + exchange on this device (all zero unless AFB_PHASE_TIMESTAMPS is set)."""
+        out = (ctypes.c_ulonglong * 8)()
+        self.check(self.lib.afb_phase_timestamps(out), "afb_phase_timestamps")
         return list(out)
 
     def launch_count(self):

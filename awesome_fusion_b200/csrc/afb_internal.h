@@ -27,10 +27,16 @@ struct DeviceCtx {
     Workspace workspaces[kMaxWorkspaces];
     size_t    splitk_ws_bytes = 0;        // size of every workspace
     size_t    splitk_counter_count = 0;   // counters of every workspace
+    // optional phase timestamps (globaltimer ns of THIS GPU) written by the row-parallel GEMM and the exchange kernel when the
+    // environment variable AFB_PHASE_TIMESTAMPS is set: [0] GEMM start, [1] GEMM end (latest CTA), [2] exchange start,
+    // [3] all ranks' GEMMs seen complete, [4] sum + broadcast done (latest CTA), [5] all ranks' blocks seen in place
+    unsigned long long* phase_ts = nullptr;
     uint32_t* ar_words = nullptr;         // device uint32[4]: hand-off words of the two exchange kernels (CTAs finished, any failed)
-    // staging for afb_gemm_host (grow-only)
-    void*  stage[4] = {nullptr, nullptr, nullptr, nullptr};
-    size_t stage_bytes[4] = {0, 0, 0, 0};
+    // staging for afb_gemm_host (grow-only): two sets used in turn, so that the copies of one call overlap the other call's
+    void*  stage[2][4] = {};
+    size_t stage_bytes[2][4] = {};
+    cudaEvent_t stage_free[2] = {};      // recorded when a call is done with its set
+    unsigned host_calls = 0;
     // copy-in / copy-out streams and per-chunk events of the pipelined afb_gemm_host
     cudaStream_t host_in = nullptr, host_out = nullptr;
     cudaEvent_t host_ev[2 * 16 + 2] = {};
@@ -43,6 +49,8 @@ struct DeviceOnce {
     bool done(int dev) const { return (mask.load(std::memory_order_acquire) >> (dev & 31)) & 1u; }
     void mark(int dev) { mask.fetch_or(1u << (dev & 31), std::memory_order_release); }
 };
+
+unsigned long long* phase_ts_if_enabled(DeviceCtx* ctx);   // ctx->phase_ts when AFB_PHASE_TIMESTAMPS is set, else nullptr
 
 DeviceCtx* current_ctx();           // nullptr when afb_init was not called on the current device
 // The split-K workspace of `s` on this device (allocates it on the stream's first use); nullptr + *rc on failure.
@@ -64,7 +72,8 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
 int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);      // converted weights through shared memory
 int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, const afb_fused_args* fused = nullptr);   // converted weights in tensor memory
 int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* tile_done, cudaStream_t s);
-int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s);
+int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s,
+                           uint32_t* const* counters = nullptr, uint32_t sub_blocks = 0);
 void prefill_ts_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* m_tiles, uint32_t* n_tiles, uint32_t* arrivals);
 int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s);
 

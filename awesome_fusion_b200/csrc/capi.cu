@@ -34,6 +34,11 @@ DeviceCtx* current_ctx() {
     return g_ctx[dev].ready ? &g_ctx[dev] : nullptr;
 }
 
+unsigned long long* phase_ts_if_enabled(DeviceCtx* ctx) {
+    static const bool on = getenv("AFB_PHASE_TIMESTAMPS") != nullptr;
+    return on ? ctx->phase_ts : nullptr;
+}
+
 const DeviceCtx::Workspace* workspace_for(DeviceCtx* ctx, cudaStream_t s, int* rc) {
     std::lock_guard<std::mutex> lock(g_mutex);
     DeviceCtx::Workspace* free_slot = nullptr;
@@ -147,6 +152,8 @@ int afb_init(int device) {
         AFB_CUDA(cudaMalloc(&c.workspaces[i].counters, kSplitKCounters * sizeof(uint32_t)));
         AFB_CUDA(cudaMemset(c.workspaces[i].counters, 0, kSplitKCounters * sizeof(uint32_t)));
     }
+    AFB_CUDA(cudaMalloc(&c.phase_ts, 8 * sizeof(unsigned long long)));
+    AFB_CUDA(cudaMemset(c.phase_ts, 0, 8 * sizeof(unsigned long long)));
     AFB_CUDA(cudaMalloc(&c.ar_words, 4 * sizeof(uint32_t)));
     AFB_CUDA(cudaMemset(c.ar_words, 0, 4 * sizeof(uint32_t)));
     AFB_CUDA(cudaDeviceSynchronize());
@@ -161,9 +168,12 @@ int afb_finalize(void) {
     DeviceCtx& c = g_ctx[dev];
     if (!c.ready) return AFB_OK;
     cudaDeviceSynchronize();
-    cudaFree(c.status); cudaFree(c.ar_words);
+    cudaFree(c.status); cudaFree(c.ar_words); cudaFree(c.phase_ts);
     for (auto& w : c.workspaces) { if (w.ws) cudaFree(w.ws); if (w.counters) cudaFree(w.counters); }
-    for (int i = 0; i < 4; ++i) if (c.stage[i]) cudaFree(c.stage[i]);
+    for (int j = 0; j < 2; ++j) {
+        for (int i = 0; i < 4; ++i) if (c.stage[j][i]) cudaFree(c.stage[j][i]);
+        if (c.stage_free[j]) cudaEventDestroy(c.stage_free[j]);
+    }
     if (c.host_in) {
         cudaStreamDestroy(c.host_in); cudaStreamDestroy(c.host_out);
         for (auto& e : c.host_ev) if (e) cudaEventDestroy(e);
@@ -299,7 +309,8 @@ static size_t b_bytes(const afb_gemm_args& a) {
     return (rows - 1) * ld_bytes + cols_bytes;  // the size rule of bfAintBGemm.cc:68-76
 }
 
-int afb_gemm_host(const afb_gemm_args* h, void* stream) {
+// wait = true: returns when C is in host memory; false: returns when everything is queued (afb_stream_sync(stream) completes it).
+static int gemm_host_impl(const afb_gemm_args* h, void* stream, bool wait) {
     int rc = validate(h);
     if (rc) return rc;
     DeviceCtx* ctx = current_ctx();
@@ -309,36 +320,44 @@ int afb_gemm_host(const afb_gemm_args* h, void* stream) {
     const size_t scale_cnt = h->group_size ? (size_t)h->n * (h->k / h->group_size) : h->n;
     const size_t need[4] = {((size_t)(h->m - 1) * h->ldc + h->n) * c_elt, ((size_t)(h->m - 1) * h->lda + h->k) * 2,
                             b_bytes(*h), scale_cnt * scale_elt};
+    if (h->ptr_zero) return AFB_ERR_UNSUPPORTED;   // zero-points: copy them yourself and use afb_gemm_launch
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!ctx->host_in) {
+        AFB_CUDA(cudaStreamCreateWithFlags(&ctx->host_in, cudaStreamNonBlocking));
+        AFB_CUDA(cudaStreamCreateWithFlags(&ctx->host_out, cudaStreamNonBlocking));
+        for (auto& e : ctx->host_ev) AFB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        for (auto& e : ctx->stage_free) AFB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    // two staging sets used in turn: this call's copies may run while the previous call (on the other set) still computes
+    // or copies out; the set's previous user, two calls back, must be done with it
+    const unsigned set = ctx->host_calls++ & 1u;
+    void** stage = ctx->stage[set];
     for (int i = 0; i < 4; ++i) {
-        if (ctx->stage_bytes[i] < need[i]) {
-            if (ctx->stage[i]) AFB_CUDA(cudaFree(ctx->stage[i]));
-            ctx->stage[i] = nullptr; ctx->stage_bytes[i] = 0;
-            AFB_CUDA(cudaMalloc(&ctx->stage[i], need[i]));
-            ctx->stage_bytes[i] = need[i];
+        if (ctx->stage_bytes[set][i] < need[i]) {
+            if (stage[i]) AFB_CUDA(cudaFree(stage[i]));   // waits for everything in flight
+            stage[i] = nullptr; ctx->stage_bytes[set][i] = 0;
+            AFB_CUDA(cudaMalloc(&stage[i], need[i]));
+            ctx->stage_bytes[set][i] = need[i];
         }
     }
-    cudaStream_t s = (cudaStream_t)stream;
+    AFB_CUDA(cudaStreamWaitEvent(s, ctx->stage_free[set], 0));
     afb_gemm_args d = *h;
-    d.ptr_c = ctx->stage[0]; d.ptr_a = ctx->stage[1]; d.ptr_b = ctx->stage[2]; d.ptr_scale = ctx->stage[3];
+    d.ptr_c = stage[0]; d.ptr_a = stage[1]; d.ptr_b = stage[2]; d.ptr_scale = stage[3];
 
     // Pipelined form for B in [N,K] layout with per-channel scales: the channels are cut into chunks; while chunk i is
     // multiplied, chunk i+1 of the weights travels host -> device and chunk i-1 of C travels device -> host (PCIe is full duplex).
     constexpr uint32_t kChunks = 8;
     const bool pipelined = h->b_layout != AFB_LAYOUT_ROW && h->group_size == 0 && h->m > 16 && h->n >= kChunks * 512 && h->n % (kChunks * 128) == 0;
     if (!pipelined) {
-        AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, s));
-        AFB_CUDA(cudaMemcpyAsync(ctx->stage[2], h->ptr_b, need[2], cudaMemcpyHostToDevice, s));
-        AFB_CUDA(cudaMemcpyAsync(ctx->stage[3], h->ptr_scale, need[3], cudaMemcpyHostToDevice, s));
+        AFB_CUDA(cudaMemcpyAsync(stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, s));
+        AFB_CUDA(cudaMemcpyAsync(stage[2], h->ptr_b, need[2], cudaMemcpyHostToDevice, s));
+        AFB_CUDA(cudaMemcpyAsync(stage[3], h->ptr_scale, need[3], cudaMemcpyHostToDevice, s));
         rc = afb_gemm_launch(&d, stream);
         if (rc) return rc;
-        AFB_CUDA(cudaMemcpyAsync(h->ptr_c, ctx->stage[0], need[0], cudaMemcpyDeviceToHost, s));
-        AFB_CUDA(cudaStreamSynchronize(s));
+        AFB_CUDA(cudaMemcpyAsync(h->ptr_c, stage[0], need[0], cudaMemcpyDeviceToHost, s));
+        AFB_CUDA(cudaEventRecord(ctx->stage_free[set], s));
+        if (wait) AFB_CUDA(cudaStreamSynchronize(s));
         return AFB_OK;
-    }
-    if (!ctx->host_in) {
-        AFB_CUDA(cudaStreamCreateWithFlags(&ctx->host_in, cudaStreamNonBlocking));
-        AFB_CUDA(cudaStreamCreateWithFlags(&ctx->host_out, cudaStreamNonBlocking));
-        for (auto& e : ctx->host_ev) AFB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
     cudaEvent_t* ev_in = ctx->host_ev;                 // [kChunks]: chunk i of B and scale is on the device
     cudaEvent_t* ev_mm = ctx->host_ev + 16;            // [kChunks]: chunk i of C is computed
@@ -346,32 +365,49 @@ int afb_gemm_host(const afb_gemm_args* h, void* stream) {
     AFB_CUDA(cudaEventRecord(ev_start, s));            // everything below happens after what the caller queued on `stream`
     AFB_CUDA(cudaStreamWaitEvent(ctx->host_in, ev_start, 0));
     AFB_CUDA(cudaStreamWaitEvent(ctx->host_out, ev_start, 0));
-    AFB_CUDA(cudaMemcpyAsync(ctx->stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, ctx->host_in));
+    AFB_CUDA(cudaMemcpyAsync(stage[1], h->ptr_a, need[1], cudaMemcpyHostToDevice, ctx->host_in));
     const uint32_t nc = h->n / kChunks;
     const size_t ldb_bytes = (size_t)h->ldb * h->b_bits / 8, b_chunk = (size_t)nc * ldb_bytes;
     for (uint32_t i = 0; i < kChunks; ++i) {
         const size_t b_off = (size_t)i * b_chunk;
         const size_t b_len = i + 1 < kChunks ? b_chunk : need[2] - b_off;
-        AFB_CUDA(cudaMemcpyAsync((char*)ctx->stage[2] + b_off, (const char*)h->ptr_b + b_off, b_len, cudaMemcpyHostToDevice, ctx->host_in));
-        AFB_CUDA(cudaMemcpyAsync((char*)ctx->stage[3] + (size_t)i * nc * scale_elt, (const char*)h->ptr_scale + (size_t)i * nc * scale_elt,
+        AFB_CUDA(cudaMemcpyAsync((char*)stage[2] + b_off, (const char*)h->ptr_b + b_off, b_len, cudaMemcpyHostToDevice, ctx->host_in));
+        AFB_CUDA(cudaMemcpyAsync((char*)stage[3] + (size_t)i * nc * scale_elt, (const char*)h->ptr_scale + (size_t)i * nc * scale_elt,
                                  (size_t)nc * scale_elt, cudaMemcpyHostToDevice, ctx->host_in));
         AFB_CUDA(cudaEventRecord(ev_in[i], ctx->host_in));
         AFB_CUDA(cudaStreamWaitEvent(s, ev_in[i], 0));
         afb_gemm_args c = d;
         c.n = nc;
-        c.ptr_b = (char*)ctx->stage[2] + b_off;
-        c.ptr_scale = (char*)ctx->stage[3] + (size_t)i * nc * scale_elt;
-        c.ptr_c = (char*)ctx->stage[0] + (size_t)i * nc * c_elt;
+        c.ptr_b = (char*)stage[2] + b_off;
+        c.ptr_scale = (char*)stage[3] + (size_t)i * nc * scale_elt;
+        c.ptr_c = (char*)stage[0] + (size_t)i * nc * c_elt;
         rc = afb_gemm_launch(&c, stream);
         if (rc) return rc;
         AFB_CUDA(cudaEventRecord(ev_mm[i], s));
         AFB_CUDA(cudaStreamWaitEvent(ctx->host_out, ev_mm[i], 0));
-        AFB_CUDA(cudaMemcpy2DAsync((char*)h->ptr_c + (size_t)i * nc * c_elt, (size_t)h->ldc * c_elt, (char*)ctx->stage[0] + (size_t)i * nc * c_elt,
+        AFB_CUDA(cudaMemcpy2DAsync((char*)h->ptr_c + (size_t)i * nc * c_elt, (size_t)h->ldc * c_elt, (char*)stage[0] + (size_t)i * nc * c_elt,
                                    (size_t)h->ldc * c_elt, (size_t)nc * c_elt, h->m, cudaMemcpyDeviceToHost, ctx->host_out));
     }
     AFB_CUDA(cudaEventRecord(ev_end, ctx->host_out));
-    AFB_CUDA(cudaStreamWaitEvent(s, ev_end, 0));
-    AFB_CUDA(cudaStreamSynchronize(s));
+    if (wait) {
+        AFB_CUDA(cudaStreamWaitEvent(s, ev_end, 0));
+        AFB_CUDA(cudaEventRecord(ctx->stage_free[set], s));
+        AFB_CUDA(cudaStreamSynchronize(s));
+    } else {
+        // `stream` must not wait for the copy-out here, or the next call's GEMMs would queue behind it: the set is released,
+        // and completion is reported, on the copy-out stream; afb_gemm_host_wait joins it
+        AFB_CUDA(cudaEventRecord(ctx->stage_free[set], ctx->host_out));
+    }
+    return AFB_OK;
+}
+
+int afb_gemm_host(const afb_gemm_args* h, void* stream) { return gemm_host_impl(h, stream, true); }
+int afb_gemm_host_async(const afb_gemm_args* h, void* stream) { return gemm_host_impl(h, stream, false); }
+int afb_gemm_host_wait(void* stream) {
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    AFB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (ctx->host_out) AFB_CUDA(cudaStreamSynchronize(ctx->host_out));
     return AFB_OK;
 }
 
@@ -400,6 +436,16 @@ int afb_read_status(int32_t out[4]) {
             if (w.counters) AFB_CUDA(cudaMemset(w.counters, 0, ctx->splitk_counter_count * sizeof(uint32_t)));
         AFB_CUDA(cudaMemset(ctx->ar_words, 0, 4 * sizeof(uint32_t)));
     }
+    return AFB_OK;
+}
+
+int afb_phase_timestamps(unsigned long long out[8]) {
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    if (!out) return AFB_ERR_BAD_ARG;
+    AFB_CUDA(cudaDeviceSynchronize());
+    AFB_CUDA(cudaMemcpy(out, ctx->phase_ts, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    AFB_CUDA(cudaMemset(ctx->phase_ts, 0, 8 * sizeof(unsigned long long)));
     return AFB_OK;
 }
 

@@ -16,6 +16,7 @@ namespace afb {
 namespace {
 
 constexpr int kThreads = 512;
+constexpr uint32_t BNW_TILE = 128;   // channels per GEMM tile (prefill_ts.cu)
 
 struct ARParams {
     const void* partial[AFB_MAX_RANKS];
@@ -26,6 +27,7 @@ struct ARParams {
     unsigned long long wait_ns;
     uint32_t* cta_done;   // local counter, zero between launches
     int32_t* status;
+    unsigned long long* ts;   // optional phase timestamps (nullptr = off)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -74,10 +76,12 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
     const uint32_t* my_sig = p.signals[p.rank];
     if (threadIdx.x == 0) {
         if (blockIdx.x == 0) {
+            if (p.ts) p.ts[2] = now_ns();
             __threadfence_system();
             for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 0 * AFB_MAX_RANKS + p.rank, p.epoch);
         }
         const bool ok = wait_all(my_sig, 0, p.world, p.epoch, p.wait_ns);
+        if (p.ts && blockIdx.x == 0) p.ts[3] = now_ns();
         if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 10; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
         if (!ok) atomicExch(p.cta_done + 1, 1u);   // every CTA runs its own clock: one that gave up vetoes the completion signal
         s_ok = ok ? 1u : 0u;
@@ -138,11 +142,106 @@ __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARPara
     if (s_last && threadIdx.x == 0) {
         const bool any_failed = atomicExch(p.cta_done + 1, 0u) != 0;
         *p.cta_done = 0u;
+        if (p.ts) p.ts[4] = now_ns();
         __threadfence_system();
         if (!any_failed) {   // after a timeout in ANY CTA part of the block was not stored: do not claim completion
             for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 1 * AFB_MAX_RANKS + p.rank, p.epoch);
             const bool ok = wait_all(my_sig, 1, p.world, p.epoch, p.wait_ns);
+            if (p.ts) p.ts[5] = now_ns();
             if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 11; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Pipelined form: runs NEXT TO the pushing GEMM (launched on another stream).  The GEMM delivers the partial sums column
+// chunk by column chunk: after every `world` units of its tile order one more chunk of THIS rank's rows is complete in the
+// local staging slots, and the GEMM has counted every tile of it in counters[chunk].  This kernel waits for a chunk's count,
+// adds the `world` LOCAL slots in rank order, rounds once and broadcasts the bf16 rows (multimem.st or peer stores), while the
+// GEMM computes the next chunk: only the last chunk's sum and broadcast remain after the GEMM.  It reads no peer memory.
+// ---------------------------------------------------------------------------------------------------------
+struct SubARParams {
+    ARParams ar;
+    const uint32_t* counters;   // local, one per column chunk, only grow
+    uint32_t sub_blocks, want;  // want = counts per chunk and launch x launches so far
+};
+
+__global__ void __launch_bounds__(128, 6) ksplit_sub_allreduce_kernel(const SubARParams sp) {
+    const ARParams& p = sp.ar;
+    __shared__ uint32_t s_ok;
+    __shared__ uint32_t s_last;
+    const uint32_t r0 = (uint32_t)((uint64_t)p.m * p.rank / p.world), r1 = (uint32_t)((uint64_t)p.m * (p.rank + 1) / p.world);
+    const uint32_t chunk_cols = p.n / sp.sub_blocks, vec_per_row = chunk_cols / 8;
+    const uint64_t total = (uint64_t)(r1 - r0) * vec_per_row;
+    bool failed = false;
+    if (p.ts && blockIdx.x == 0 && threadIdx.x == 0) p.ts[2] = now_ns();
+    for (uint32_t c = 0; c < sp.sub_blocks && !failed; ++c) {
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = now_ns();
+            bool ok = true;
+            uint32_t spins = 0;
+            while ((int32_t)(ld_acquire_sys(sp.counters + c) - sp.want) < 0) {
+                if ((++spins & 0xfu) == 0) {
+                    if (now_ns() - t0 > p.wait_ns) { ok = false; break; }
+                    __nanosleep(200);
+                }
+            }
+            if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 14; p.status[2] = (int)c; p.status[3] = (int)p.epoch; }
+            s_ok = ok ? 1u : 0u;
+            if (p.ts && blockIdx.x == 0 && c + 1 == sp.sub_blocks) p.ts[3] = now_ns();
+        }
+        __syncthreads();
+        if (!s_ok) { failed = true; break; }
+        for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+            const uint32_t row = r0 + (uint32_t)(i / vec_per_row), col = c * chunk_cols + (uint32_t)(i % vec_per_row) * 8;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            // four slots at a time: few registers, so that a CTA of this kernel fits next to the GEMM's CTA on an SM
+#pragma unroll
+            for (int q0 = 0; q0 < AFB_MAX_RANKS; q0 += 4) {
+                uint4 lo[4], hi[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (q0 + q < (int)p.world) {
+                        const float* src = reinterpret_cast<const float*>(p.partial[q0 + q]) + (size_t)row * p.ld_partial + col;
+                        lo[q] = __ldcg(reinterpret_cast<const uint4*>(src)); hi[q] = __ldcg(reinterpret_cast<const uint4*>(src + 4));
+                    }
+#pragma unroll
+                for (int q = 0; q < 4; ++q)   // fixed rank order: identical bits wherever it is computed
+                    if (q0 + q < (int)p.world) {
+                        acc[0] += __uint_as_float(lo[q].x); acc[1] += __uint_as_float(lo[q].y); acc[2] += __uint_as_float(lo[q].z); acc[3] += __uint_as_float(lo[q].w);
+                        acc[4] += __uint_as_float(hi[q].x); acc[5] += __uint_as_float(hi[q].y); acc[6] += __uint_as_float(hi[q].z); acc[7] += __uint_as_float(hi[q].w);
+                    }
+            }
+            const uint4 out = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+            if (p.c_multicast) {
+                st16_multicast(p.c_multicast + (size_t)row * p.ldc + col, out);
+            } else {
+#pragma unroll
+                for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                    if (q < (int)p.world) *reinterpret_cast<uint4*>(p.c[q] + (size_t)row * p.ldc + col) = out;
+            }
+        }
+        __syncthreads();   // s_ok is rewritten for the next chunk
+    }
+    // the last CTA to finish tells every rank that this rank's rows are in place, then waits for theirs
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (failed) atomicExch(p.cta_done + 1, 1u);
+        const uint32_t old = atomicAdd(p.cta_done, 1u);
+        s_last = old == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        const bool any_failed = atomicExch(p.cta_done + 1, 0u) != 0;
+        *p.cta_done = 0u;
+        if (p.ts) p.ts[4] = now_ns();
+        __threadfence_system();
+        if (!any_failed) {
+            for (uint32_t q = 0; q < p.world; ++q) st_release_sys(p.signals[q] + 1 * AFB_MAX_RANKS + p.rank, p.epoch);
+            const bool ok = wait_all(p.signals[p.rank], 1, p.world, p.epoch, p.wait_ns);
+            if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 15; p.status[2] = (int)p.rank; p.status[3] = (int)p.epoch; }
+            if (p.ts) p.ts[5] = now_ns();
         }
     }
 }
@@ -287,6 +386,7 @@ extern "C" int afb_ksplit_allreduce_launch(const afb_allreduce_args* a, void* st
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
     p.cta_done = ctx->ar_words;          // words 0-1: this kernel
     p.status = ctx->status;
+    p.ts = phase_ts_if_enabled(ctx);
     const int grid = ctx->sm_count;   // one CTA per SM: all CTAs are co-resident, so the last-CTA hand-off cannot starve
     if (a->partial_f32) ksplit_allreduce_kernel<true><<<grid, kThreads, 0, (cudaStream_t)stream>>>(p);
     else                ksplit_allreduce_kernel<false><<<grid, kThreads, 0, (cudaStream_t)stream>>>(p);
@@ -352,6 +452,76 @@ extern "C" int afb_gemm_launch_push(const afb_gemm_args* args, void* const stage
     return launch_prefill_ts_push(a, ctx, stage, world, rank, (cudaStream_t)stream);
 }
 
+extern "C" int afb_gemm_launch_push_pipelined(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t* const counters[AFB_MAX_RANKS],
+                                              uint32_t world, uint32_t rank, uint32_t sub_blocks, void* stream) {
+    if (!args || !stage || !counters || !args->ptr_a || !args->ptr_b || !args->ptr_scale) return AFB_ERR_BAD_ARG;
+    if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;
+    if (args->lda < args->k || args->ldb < args->k || args->b_layout == AFB_LAYOUT_ROW || args->b_layout > 2) return AFB_ERR_BAD_ARG;
+    if (!(args->flags & AFB_FLAG_C_F32)) return AFB_ERR_UNSUPPORTED;   // the partial sums travel as fp32
+    if (world == 0 || world > AFB_MAX_RANKS || rank >= world || sub_blocks == 0) return AFB_ERR_BAD_ARG;
+    for (uint32_t q = 0; q < world; ++q) if (!stage[q] || (uintptr_t)stage[q] % 16 || !counters[q]) return AFB_ERR_BAD_ARG;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    afb_gemm_args a = *args;
+    a.ptr_c = stage[rank];   // never written in this mode; keeps the common validation happy
+    a.ldc = a.n;
+    return launch_prefill_ts_push(a, ctx, stage, world, rank, (cudaStream_t)stream, counters, sub_blocks);
+}
+
+extern "C" int afb_ksplit_sub_info(uint32_t m, uint32_t n, uint32_t world, uint32_t sub_blocks, uint32_t* counts_per_chunk) {
+    if (!counts_per_chunk || world == 0 || sub_blocks == 0 || m % (256 * world) || n % (BNW_TILE * sub_blocks)) return AFB_ERR_BAD_ARG;
+    uint32_t tm, tn, mt, nt, arr;
+    prefill_ts_tile_info(m, n, &tm, &tn, &mt, &nt, &arr);
+    *counts_per_chunk = (mt / world) * (nt / sub_blocks) * world * arr;   // tiles of a chunk of one owner's rows x ranks x counts per tile
+    return AFB_OK;
+}
+
+extern "C" int afb_ksplit_sub_allreduce_launch(const afb_sub_allreduce_args* sa, void* stream) {
+    if (!sa) return AFB_ERR_BAD_ARG;
+    const afb_allreduce_args* a = &sa->base;
+    if (a->world == 0 || a->world > AFB_MAX_RANKS || a->rank >= a->world) return AFB_ERR_BAD_ARG;
+    if (a->m == 0 || a->n == 0 || a->ldc % 8 || a->ld_partial % 8 || a->ld_partial < a->n || a->ldc < a->n) return AFB_ERR_BAD_ARG;
+    if (a->epoch == 0 || a->reserved != 0 || !a->partial_f32 || !sa->counters || sa->sub_blocks == 0 || sa->launches == 0 || sa->reserved != 0) return AFB_ERR_BAD_ARG;
+    uint32_t per_chunk = 0;
+    if (afb_ksplit_sub_info(a->m, a->n, a->world, sa->sub_blocks, &per_chunk) != AFB_OK) return AFB_ERR_UNSUPPORTED;
+    for (uint32_t q = 0; q < a->world; ++q) {
+        if (!a->partial[q] || !a->c[q] || !a->signals[q]) return AFB_ERR_BAD_ARG;
+        if ((uintptr_t)a->partial[q] % 16 || (uintptr_t)a->c[q] % 16) return AFB_ERR_BAD_ARG;
+    }
+    if ((uintptr_t)a->c_multicast % 16) return AFB_ERR_BAD_ARG;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    SubARParams sp;
+    ARParams& p = sp.ar;
+    for (int q = 0; q < AFB_MAX_RANKS; ++q) {
+        const bool on = q < (int)a->world;
+        p.partial[q] = on ? a->partial[q] : nullptr;
+        p.c[q] = on ? reinterpret_cast<uint16_t*>(a->c[q]) : nullptr;
+        p.signals[q] = on ? a->signals[q] : nullptr;
+    }
+    p.rank = a->rank; p.world = a->world; p.m = a->m; p.n = a->n; p.ld_partial = a->ld_partial; p.ldc = a->ldc;
+    p.partial_f32 = 1; p.epoch = a->epoch;
+    p.c_multicast = reinterpret_cast<uint16_t*>(a->c_multicast);
+    p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
+    p.cta_done = ctx->ar_words + 2;      // shares the pair of the tile-granular kernel: the two forms are never used together
+    p.status = ctx->status;
+    p.ts = phase_ts_if_enabled(ctx);
+    sp.counters = sa->counters; sp.sub_blocks = sa->sub_blocks; sp.want = per_chunk * sa->launches;
+    // next to the GEMM's CTA on an SM: same shared-memory carve-out as the GEMM, or the two never co-reside (see the tile-granular form)
+    static DeviceOnce carveout_set;
+    if (!carveout_set.done(ctx->device)) {
+        cudaError_t e = cudaFuncSetAttribute(ksplit_sub_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return cuda_fail(e);
+        carveout_set.mark(ctx->device);
+    }
+    // 128 threads with at most 80 registers each (launch bounds): 10 240 registers, which fit next to the GEMM's 320 x 168
+    static const int ctas = [] { const char* e = getenv("AFB_SUB_AR_CTAS"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 148) ? v : 64; }();
+    ksplit_sub_allreduce_kernel<<<ctas, 128, 0, (cudaStream_t)stream>>>(sp);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AFB_OK : cuda_fail(e);
+}
+
 extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* ta, void* stream) {
     if (!ta) return AFB_ERR_BAD_ARG;
     const afb_allreduce_args* a = &ta->base;
@@ -381,6 +551,7 @@ extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* t
     p.wait_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
     p.cta_done = ctx->ar_words + 2;      // words 2-3: the tile-granular kernel may overlap the plain one
     p.status = ctx->status;
+    p.ts = nullptr;
     tp.tile_m = tm; tp.tile_n = tn; tp.m_tiles = mt; tp.n_tiles = nt; tp.arrivals = arr; tp.tile_epoch = ta->tile_epoch;
     // One CTA per SM next to the GEMM's CTA (256 threads, no dynamic shared memory, <= 128 registers per thread).
     // The GEMM needs the SM's largest shared-memory carve-out; an SM cannot change its carve-out while a CTA is resident,

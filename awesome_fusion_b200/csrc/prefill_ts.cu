@@ -66,9 +66,15 @@ struct TsParams {
     uint32_t fused;        // 0: off; bit 0: on; bit 1: gated
     uint32_t act;          // AFB_ACT_*
     uint32_t push_rows, push_rank;
+    // optional (pipelined reduce-scatter): the tiles are taken in units of (owner's row tiles) x (n_tiles / push_sub channel tiles);
+    // unit u covers column chunk u / world of the rows of owner (rank + u % world) % world, so that after every `world` units one
+    // more column chunk is complete on EVERY owner.  Each finished tile is counted in push_cnt[owner][chunk] (system-scope release).
+    uint32_t push_sub, push_world;
+    uint32_t* push_cnt[AFB_MAX_RANKS];
     uint32_t push_on;      // 0: off; 1: the epilogue stores to the owner directly; 2: the epilogue stores to p.c (local) and the
                            // forwarder warps copy each finished tile to its owner while the next tile is being computed
     int32_t* status;
+    unsigned long long* ts;   // optional phase timestamps: [0] start of CTA 0, [1] latest end of any CTA (nullptr = off)
 };
 
 template <int BITS, int BMA>
@@ -90,6 +96,14 @@ struct TsLayout {
 // Tile t -> (row tile, channel tile).  Consecutive tiles (= the CTAs of one wave) share group_m activation row tiles and
 // walk the channel tiles, so the activations of a group stay in L2 while the weights stream past once per group.
 __device__ __forceinline__ void tile_coords(const TsParams& p, uint32_t t, uint32_t& m_tile, uint32_t& n_tile) {
+    if (p.push_sub) {
+        const uint32_t rt = p.m_tiles / p.push_world, cn = p.n_tiles / p.push_sub, per_unit = rt * cn;
+        const uint32_t u = t / per_unit, i = t - u * per_unit;
+        const uint32_t chunk = u / p.push_world, owner = (p.push_rank + (u - chunk * p.push_world)) % p.push_world;
+        n_tile = chunk * cn + i / rt;
+        m_tile = owner * rt + (i - (i / rt) * rt);
+        return;
+    }
     const uint32_t per_group = p.group_m * p.n_tiles;
     const uint32_t g = t / per_group, r = t - g * per_group;
     const uint32_t gsz = min(p.group_m, p.m_tiles - g * p.group_m);
@@ -158,6 +172,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
     };
 
     if (threadIdx.x == 0) {
+        if (p.ts && blockIdx.x == 0) p.ts[0] = ptx::globaltimer();
         for (int s = 0; s < S; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty_act(s), 1); ptx::mbar_init(bar_empty_raw(s), kWorkerWarps); }
         for (int s = 0; s < kSlotsA; ++s) { ptx::mbar_init(bar_full_a(s), kWorkerWarps); ptx::mbar_init(bar_empty_a(s), 1); }
         ptx::mbar_init(bar_acc_full, 1);
@@ -503,10 +518,16 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                     if (tid == 0) p.tail_counters[w.tail_r] = 0u;   // ready for the next launch
                 }
             }
+            if (p.push_sub) __threadfence_system();   // this lane's peer stores of the tile are visible system-wide before the count below
+            if (p.push_sub) __syncwarp();
             if (lane == 0) {
                 ptx::mbar_arrive(bar_acc_empty);
                 if (p.push_on == 2) ptx::mbar_arrive(bar_tile_stored);
                 if (p.tile_done) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.tile_done + t), "r"(1u) : "memory");
+                if (p.push_sub) {   // one count per converter warp and tile, at the owner of the tile's rows, for the tile's column chunk
+                    const uint32_t owner = m0 / p.push_rows, chunk = nt_ / (p.n_tiles / p.push_sub);
+                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_cnt[owner] + chunk), "r"(1u) : "memory");
+                }
             }
         }
     }
@@ -547,6 +568,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
     // ---- teardown: every thread gets here, also after an abort ----
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (p.ts && threadIdx.x == 0) atomicMax(p.ts + 1, ptx::globaltimer());
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, L::kTmemCols);
@@ -596,7 +618,8 @@ uint32_t pick_group_m(const afb_gemm_args& a, uint32_t m_tiles, uint32_t n_tiles
 
 template <int BITS, bool GROUPED, int BMA>
 int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr, void* const* push = nullptr,
-                  uint32_t push_world = 0, uint32_t push_rank = 0, bool push_via_local = false, const afb_fused_args* fused = nullptr) {
+                  uint32_t push_world = 0, uint32_t push_rank = 0, bool push_via_local = false, const afb_fused_args* fused = nullptr,
+                  uint32_t* const* push_cnt = nullptr, uint32_t push_sub = 0) {
     using L = TsLayout<BITS, BMA>;
     static_assert(L::kDynamic <= 232448, "shared memory budget");
     CUtensorMap ta, tw;
@@ -656,9 +679,14 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
         if (!(e && atoi(e) == 0)) p.m_rot = (uint32_t)(((uint64_t)push_rank * p.m_tiles) / push_world) % p.m_tiles;
     }
     p.push_rank = push_rank;
+    p.push_world = push_world;
+    p.push_sub = (push && push_cnt) ? push_sub : 0;
+    for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push_cnt[q] = (p.push_sub && q < push_world) ? push_cnt[q] : nullptr;
+    if (p.push_sub) p.m_rot = 0;   // the unit order already spreads the owners
     p.push_rows = push ? a.m / push_world : 0;
     for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push[q] = (push && q < push_world) ? reinterpret_cast<float*>(push[q]) : nullptr;
     p.status = ctx->status;
+    p.ts = push ? phase_ts_if_enabled(ctx) : nullptr;
     auto kern = prefill_ts_kernel<BITS, GROUPED, BMA>;
     static DeviceOnce attr_set;  // per template instance
     if (!attr_set.done(ctx->device)) {
@@ -689,10 +717,15 @@ int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* ti
 
 // Row-parallel GEMM whose epilogue is the reduce-scatter: every tile of fp32 partial sums is stored straight into the staging
 // buffer of the rank that owns those rows (peer stores over NVLink), slot = this rank.
-int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s) {
+int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s,
+                           uint32_t* const* counters, uint32_t sub_blocks) {
     if (!prefill_supports(a) || a.group_size != 0 || a.b_bits != 8 || a.m <= 128) return AFB_ERR_UNSUPPORTED;
     if (world == 0 || world > AFB_MAX_RANKS || rank >= world || a.m % (world * 256) != 0 || a.ldc != a.n) return AFB_ERR_UNSUPPORTED;
-    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank, (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) != 0);
+    if (counters) {   // pipelined form: whole column chunks of channel tiles, epilogue stores straight to the owner
+        const uint32_t n_tiles = (a.n + BNW - 1) / BNW;
+        if (sub_blocks == 0 || n_tiles % sub_blocks != 0 || a.n % BNW != 0 || (a.flags & AFB_FLAG_PUSH_VIA_LOCAL)) return AFB_ERR_UNSUPPORTED;
+    }
+    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank, (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) != 0, nullptr, counters, sub_blocks);
 }
 
 // `fused`: optional epilogue description (bias, activation, gate * up, residual); a.ptr_c / a.ldc describe the [M, N_out] result.

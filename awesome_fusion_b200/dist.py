@@ -55,6 +55,12 @@ class TileAllReduceArgs(ctypes.Structure):
     _fields_ = [("base", AllReduceArgs), ("tile_done", ctypes.c_void_p * MAX_RANKS), ("tile_epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
+class SubAllReduceArgs(ctypes.Structure):
+    """``afb_sub_allreduce_args`` of include/afb_capi.h."""
+    _fields_ = [("base", AllReduceArgs), ("counters", ctypes.c_void_p), ("sub_blocks", ctypes.c_uint32), ("launches", ctypes.c_uint32),
+                ("reserved", ctypes.c_uint32)]
+
+
 def push_slot_offset(q, rank, world, m, n):
     """Byte offset, from the start of rank `rank`'s staging buffer float[world][m / world][n], of the address that the exchange
     kernel must be given as partial[q] so that its absolute-row indexing (rows rank*m/world .. of an [m, n] matrix) lands in slot q."""
@@ -198,6 +204,34 @@ class PeerExchange:
         self.lib.lib.afb_ksplit_allreduce_launch.argtypes = [ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
         self.lib.check(self.lib.lib.afb_ksplit_allreduce_launch(ctypes.byref(a), stream), "afb_ksplit_allreduce_launch")
 
+    def pipelined_supported(self, sub_blocks):
+        return self.push_supported() and self.n % (128 * sub_blocks) == 0 and sub_blocks <= self.num_tiles
+
+    def gemm_pushing_pipelined(self, args, sub_blocks, stream=None):
+        """The pushing GEMM in column-chunk order, counting finished tiles at their owners (the per-tile counter buffers of
+        this object serve as the per-chunk counters: one form per object)."""
+        from .capi import GemmArgs
+        f = self.lib.lib.afb_gemm_launch_push_pipelined
+        f.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint32, ctypes.c_uint32,
+                      ctypes.c_uint32, ctypes.c_void_p]
+        stage = (ctypes.c_void_p * MAX_RANKS)(*[self.partials[q] for q in range(self.world)])
+        cnt = (ctypes.c_void_p * MAX_RANKS)(*[self.tds[q] for q in range(self.world)])
+        self.lib.check(f(ctypes.byref(args), stage, cnt, self.world, self.rank, sub_blocks, stream), "afb_gemm_launch_push_pipelined")
+        self.sub_launches = getattr(self, "sub_launches", 0) + 1
+
+    def allreduce_pipelined(self, sub_blocks, stream=None):
+        """Chunk-by-chunk sum of the local slots + broadcast; launch it on another stream than gemm_pushing_pipelined()."""
+        self.epoch += 1
+        sa = SubAllReduceArgs()
+        sa.base = self.args()
+        sa.base.epoch = self.epoch
+        for q in range(self.world):
+            sa.base.partial[q] = self.partial + push_slot_offset(q, self.rank, self.world, self.m, self.n)
+        sa.counters, sa.sub_blocks, sa.launches, sa.reserved = self.tile_done, sub_blocks, self.sub_launches, 0
+        f = self.lib.lib.afb_ksplit_sub_allreduce_launch
+        f.argtypes = [ctypes.POINTER(SubAllReduceArgs), ctypes.c_void_p]
+        self.lib.check(f(ctypes.byref(sa), stream), "afb_ksplit_sub_allreduce_launch")
+
     def gemm_publishing_tiles(self, args, stream=None):
         """The K-split GEMM into this rank's partial-sum buffer, counting finished tiles for allreduce_tiles()."""
         f = self.lib.lib.afb_gemm_launch_tiles
@@ -265,6 +299,7 @@ class ShardedMLP:
         self.b_down = torch.randint(-127, 128, (down_n, self.down_k_local), generator=gr, device=dev, dtype=torch.int8)
         self.s_down = torch.rand((down_n,), generator=g, device=dev) * 0.009 + 0.001   # scales are per output channel: replicated
         self.flops_per_step_global = 2.0 * m * up_n * up_k + 2.0 * m * down_n * down_k
+        self.layout = pkg.LAYOUT_COL
         self.args_up = lib.make_args(self.c_up, self.a_up, self.b_up, self.s_up, m, self.up_n_local, up_k)
         self.px = None
         if world == 1:
@@ -281,6 +316,13 @@ class ShardedMLP:
             mode = "push" if (partial == "f32" and m % (256 * world) == 0) else "fused"
         self.overlap = mode == "overlap"
         self.push = mode == "push"
+        self.pipelined = mode == "pipelined"
+        self.sub_blocks = int(os.environ.get("AFB_SUB_BLOCKS", "8"))
+        if mode == "pipelined":
+            if partial != "f32" or m % (256 * world) != 0 or down_n % (128 * self.sub_blocks) != 0:
+                raise pkg.AfbError(-4, "the pipelined exchange needs fp32 partial sums, M a multiple of 256 * world and N of 128 * sub-blocks", "")
+            mode = "fused"
+            self.side = torch.cuda.Stream()
         if mode == "overlap":
             mode = "fused"
             self.side = torch.cuda.Stream()
@@ -295,13 +337,15 @@ class ShardedMLP:
                 self.px.close(); self.px = None
                 self.overlap = False
                 self.push = False
-                if exchange in ("fused", "overlap", "push"):
+                self.pipelined = False
+                if exchange in ("fused", "overlap", "push", "pipelined"):
                     raise pkg.AfbError(-3, "peer-memory exchange unavailable", why)
                 if rank == 0:
                     print(f"peer memory unavailable ({why}); using the NCCL exchange", flush=True)
                 mode = "nccl"
         if mode == "fused":
-            self.exchange_name = (f"tile-granular peer-memory all-reduce overlapped with the GEMM ({partial} partial sums)" if self.overlap
+            self.exchange_name = (f"reduce-scatter in the GEMM epilogue in {self.sub_blocks} column chunks (peer stores of fp32 tiles), each chunk summed from local slots and broadcast next to the GEMM" if self.pipelined
+                                  else f"tile-granular peer-memory all-reduce overlapped with the GEMM ({partial} partial sums)" if self.overlap
                                   else "reduce-scatter in the GEMM epilogue (peer stores of fp32 tiles) + local sum and bf16 broadcast" if self.push
                                   else f"fused peer-memory all-reduce after the GEMM ({partial} partial sums)")
             if self.px.c_multicast and not self.overlap:
@@ -323,6 +367,17 @@ class ShardedMLP:
             self.args_down = lib.make_args(self.partial32, self.a_down, self.b_down, self.s_down, m, down_n, self.down_k_local,
                                            flags=pkg.FLAG_C_F32)
 
+    def prepack_weights(self):
+        """Offline step: re-orders both weight shards in place into the pre-packed layout (afb_prepack) and points the GEMMs at them."""
+        lib, pkg = self.lib, self.pkg
+        if self.layout == pkg.LAYOUT_COL_PACKED:
+            return
+        for args, b in ((self.args_up, self.b_up), (self.args_down, self.b_down)):
+            lib.prepack(args, b, args.ldb)
+            args.b_layout = pkg.LAYOUT_COL_PACKED
+        self.layout = pkg.LAYOUT_COL_PACKED
+        self.torch.cuda.synchronize()
+
     def step(self, stream, events=None):
         lib = self.lib
         if events:
@@ -339,6 +394,18 @@ class ShardedMLP:
                 self.px.allreduce_tiles(self.side.cuda_stream)
                 done = self.side.record_event()
             torch.cuda.current_stream().wait_event(done)   # the step ends when C is complete on this rank
+            if events:
+                events[2].record()
+            return
+        if self.world > 1 and self.px is not None and self.pipelined:
+            torch = self.torch
+            before = torch.cuda.current_stream().record_event()
+            self.px.gemm_pushing_pipelined(self.args_down, self.sub_blocks, stream)
+            with torch.cuda.stream(self.side):      # runs next to the GEMM: chunk c is summed and broadcast while chunk c + 1 is computed
+                self.side.wait_event(before)
+                self.px.allreduce_pipelined(self.sub_blocks, self.side.cuda_stream)
+                done = self.side.record_event()
+            torch.cuda.current_stream().wait_event(done)
             if events:
                 events[2].record()
             return
@@ -393,11 +460,12 @@ class ShardedMLP:
         if self.world == 1:
             a1 = lib.make_args(c_up, host["a_up"], host["b_up"], host["s_up"], self.m, self.up_n_local, self.up_k)
             a2 = lib.make_args(c_down, host["a_down"], host["b_down"], host["s_down"], self.m, self.down_n, self.down_k_local)
-            api = "afb_gemm_host (C ABI, pinned host buffers)"
+            api = "afb_gemm_host_async x2 + afb_gemm_host_wait (C ABI, pinned host buffers)"
 
-            def one():
-                lib.gemm_host(a1)
-                lib.gemm_host(a2)
+            def one():   # the second GEMM's copy-in overlaps the first one's GEMM and copy-out
+                lib.gemm_host_async(a1)
+                lib.gemm_host_async(a2)
+                lib.gemm_host_wait()
         else:
             stream = torch.cuda.current_stream().cuda_stream
             c_down_dev = self.px.c if self.px is not None else self.c_down.data_ptr()

@@ -319,7 +319,7 @@ def parity_check(mlp, torch, world, rank):
 
     def case_of(a, b, s):
         n, k = b.shape
-        return T.Case(m=len(rows), n=n, k=k, bits=8, group=0, layout=1, enc=0, scale_dtype=0, a=to_u16(a[rows]),
+        return T.Case(m=len(rows), n=n, k=k, bits=8, group=0, layout=int(mlp.layout), enc=0, scale_dtype=0, a=to_u16(a[rows]),
                       b=b.cpu().numpy().view(np.uint8), scale=s.cpu().numpy().astype(np.float32), ldb=k)
 
     worst, worst_nrms = 0.0, 0.0
@@ -388,31 +388,33 @@ def run_ours(args):
             tdist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(warm):
-        mlp.step(stream)
-    barrier()
-    launches0 = lib.launch_count()
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    e0.record()
-    for i in range(steps):
-        mlp.step(stream, events=kev[i])
-    e1.record()
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    ms = e0.elapsed_time(e1) / steps
-    launches = lib.launch_count() - launches0
-    up_ms = sum(a.elapsed_time(b) for a, b, _ in kev) / steps
-    down_ms = sum(b.elapsed_time(c) for _, b, c in kev) / steps     # includes the exchange at N > 1
-    t = torch.tensor([ms, up_ms, down_ms, float(launches)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        tmax = t.clone(); tdist.all_reduce(tmax, op=tdist.ReduceOp.MAX)
-        tsum = t.clone(); tdist.all_reduce(tsum, op=tdist.ReduceOp.SUM)
-        ms, up_ms, down_ms = tmax[0].item(), tmax[1].item(), tmax[2].item()
-        launches = int(tsum[3].item())
+
+    def timed_run(sample_clocks):
+        """warm-up, then `steps` steps between events; returns (ms per step, up ms, down ms, launches), max over the ranks"""
+        for _ in range(warm):
+            mlp.step(stream)
+        barrier()
+        launches0 = lib.launch_count()
+        if sample_clocks and rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        e0.record()
+        for i in range(steps):
+            mlp.step(stream, events=kev[i])
+        e1.record()
+        barrier()
+        clk = sampler.stop() if (sample_clocks and rank == 0) else None
+        t = torch.tensor([e0.elapsed_time(e1) / steps, sum(a.elapsed_time(b) for a, b, _ in kev) / steps,
+                          sum(b.elapsed_time(c) for _, b, c in kev) / steps, float(lib.launch_count() - launches0)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            tmax = t.clone(); tdist.all_reduce(tmax, op=tdist.ReduceOp.MAX)
+            tsum = t.clone(); tdist.all_reduce(tsum, op=tdist.ReduceOp.SUM)
+            return tmax[0].item(), tmax[1].item(), tmax[2].item(), int(tsum[3].item()), clk
+        return t[0].item(), t[1].item(), t[2].item(), int(t[3].item()), clk
+
+    ms, up_ms, down_ms, launches, clocks = timed_run(True)      # down_ms includes the exchange at N > 1
     status = lib.read_status()
     total_flops = mlp.flops_per_step_global
     value = total_flops / ms / 1e9
@@ -426,7 +428,21 @@ def run_ours(args):
     e2e_obj = {"value": total_flops / e2e["ms"] / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": e2e["h2d"] * world,
                "d2h_bytes_per_step": e2e["d2h"] * world, "ms_per_step": e2e["ms"], "api": e2e["api"]}
 
+    phases = None
+    if world > 1 and os.environ.get("AFB_PHASE_TIMESTAMPS"):
+        # last step's device-side stamps (ns of each GPU's own timer; only differences on one GPU mean anything)
+        ts = lib.phase_timestamps()
+        mine = {"gemm_us": (ts[1] - ts[0]) / 1e3, "gemm_end_to_exchange_start_us": (ts[2] - ts[1]) / 1e3, "wait_for_all_gemms_us": (ts[3] - ts[2]) / 1e3,
+                "sum_and_broadcast_us": (ts[4] - ts[3]) / 1e3, "wait_for_all_blocks_us": (ts[5] - ts[4]) / 1e3, "total_us": (ts[5] - ts[0]) / 1e3} if ts[0] and ts[5] else None
+        phases = [None] * world
+        tdist.all_gather_object(phases, mine)
     parity = parity_check(mlp, torch, world, rank)
+    # the same step on pre-packed weights (afb_prepack is an offline step: not inside any timed region), with its own parity check
+    mlp.prepack_weights()
+    pk_ms, pk_up_ms, pk_down_ms, _, _ = timed_run(False)
+    pk_parity = parity_check(mlp, torch, world, rank)
+    parity["prepacked_run"] = {"max_rel": pk_parity["max_rel"], "nrms": pk_parity["nrms"], "ok": pk_parity["ok"]}
+    parity["ok"] = bool(parity["ok"] and pk_parity["ok"])
     shutdown(mlp, world, torch)
     if rank != 0:
         return 0 if parity["ok"] else 1
@@ -442,7 +458,12 @@ def run_ours(args):
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16xint8->fp32", "data": "synthetic",
             "config": headline_config(world), "exchange": mlp.exchange_name, "clocks": clocks, "e2e": e2e_obj, "gpu_launches": launches,
-            "roofline": roofline, "per_gemm_ms": {"up": up_ms, "down_incl_exchange": down_ms}, "device_status": status, "parity": parity}
+            "roofline": roofline, "per_gemm_ms": {"up": up_ms, "down_incl_exchange": down_ms}, "device_status": status, "parity": parity,
+            "prepacked_weights": {"value": total_flops / pk_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": pk_ms,
+                                  "per_gemm_ms": {"up": pk_up_ms, "down_incl_exchange": pk_down_ms},
+                                  "note": "same step after afb_prepack (offline re-ordering of the same integers); `value` is measured on the weights as given"}}
+    if phases:
+        line["down_projection_phases_per_rank"] = phases
     if world == 1:
         cases = []
         if not args.no_cases:
@@ -480,7 +501,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sharded-mlp", choices=["sharded-mlp"] + sorted(SINGLE_CASES))
-    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "overlap", "fused", "nccl"])
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "pipelined", "overlap", "fused", "nccl"])
     ap.add_argument("--no-cases", action="store_true", help="skip the single-GPU case sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     args = ap.parse_args()

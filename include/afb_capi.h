@@ -140,6 +140,11 @@ int afb_gemm_resolve_variant(const afb_gemm_args* args, uint32_t* variant);
  * as one call on HOST pointers: copies A, B, scale to library-owned device staging,
  * launches, copies C back, and returns when C is in host memory.                     */
 int afb_gemm_host(const afb_gemm_args* host_args, void* stream);
+/* The same without the final wait: returns when the copies and launches are queued, so that the next call's copy-in overlaps
+ * this call's GEMM and copy-out (two staging sets are used in turn; at most two calls in flight make progress at once).
+ * The host buffers must stay untouched until afb_gemm_host_wait(stream) has returned: it waits for every queued call. */
+int afb_gemm_host_async(const afb_gemm_args* host_args, void* stream);
+int afb_gemm_host_wait(void* stream);
 /* No counterpart in the reference.  The decode GEMM (M <= 16, B in [N,K] layout) for callers that must not
  * allocate: programs whose framework already owns all device memory, and latency-critical loops that cannot
  * afford the device-wide synchronisation of cudaMalloc.  Needs no afb_init and calls no cudaMalloc / cudaFree or
@@ -282,6 +287,25 @@ int afb_dist_sync(afb_dist* dist);
 int afb_dist_finalize(afb_dist* dist);
 /* [lo, hi) of `total` owned by `rank`: whole units of `multiple`, the remainder to the first ranks.  Needs no GPU. */
 int afb_dist_split_range(uint32_t total, uint32_t world, uint32_t rank, uint32_t multiple, uint32_t* lo, uint32_t* hi);
+/* Pipelined form of the epilogue reduce-scatter: the pushing GEMM takes its tiles column chunk by column chunk (the N channels
+ * cut into `sub_blocks` chunks) and, inside a chunk, owner by owner starting with its own rank, so that every `world` units one
+ * more chunk of EVERY rank's rows is complete in that rank's staging slots; each finished tile is counted in
+ * counters[owner][chunk] (uint32[sub_blocks] per rank, zero before first use, only grow).  afb_ksplit_sub_allreduce_launch,
+ * launched on ANOTHER stream so that it runs next to the GEMM, waits for a chunk's count, sums the LOCAL slots in rank order,
+ * rounds and broadcasts it while the GEMM works on the next chunk: only the last chunk is left after the GEMM.  base.partial[q]
+ * are the local slots as for afb_gemm_launch_push; base.signals / epoch as for afb_ksplit_allreduce_launch; `launches` = how
+ * many pipelined GEMMs have been issued on these counters (same on all ranks).  N must be a multiple of 128 * sub_blocks. */
+typedef struct afb_sub_allreduce_args {
+    afb_allreduce_args base;
+    uint32_t* counters;      /* this rank's counters */
+    uint32_t  sub_blocks;
+    uint32_t  launches;
+    uint32_t  reserved;
+} afb_sub_allreduce_args;
+int afb_ksplit_sub_info(uint32_t m, uint32_t n, uint32_t world, uint32_t sub_blocks, uint32_t* counts_per_chunk);
+int afb_gemm_launch_push_pipelined(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t* const counters[AFB_MAX_RANKS],
+                                   uint32_t world, uint32_t rank, uint32_t sub_blocks, void* stream);
+int afb_ksplit_sub_allreduce_launch(const afb_sub_allreduce_args* args, void* stream);
 /* sizeof(afb_gemm_args), sizeof(afb_allreduce_args), sizeof(afb_tile_allreduce_args), sizeof(afb_fused_args) as this library was
  * compiled: a binding in another language compares them with its own declarations before the first call.  Needs no GPU. */
 int afb_abi_sizes(uint32_t sizes[4]);
@@ -293,6 +317,11 @@ int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uin
 const char* afb_status_string(int status);
 int afb_last_cuda_error(void);             /* cudaError_t of the last failing CUDA call */
 const char* afb_last_cuda_error_string(void);
+/* Phase timestamps of the last row-parallel GEMM + exchange on the current device (measurement aid; written only while the
+ * environment variable AFB_PHASE_TIMESTAMPS is set).  Nanoseconds of this GPU's own timer: out[0] GEMM start, [1] GEMM end,
+ * [2] exchange kernel start, [3] every rank's GEMM seen complete, [4] sum and broadcast done, [5] every rank's block seen in
+ * place.  Synchronises the device and clears the record. */
+int afb_phase_timestamps(unsigned long long out[8]);
 /* Number of kernels this library launched since afb_init (all variants). */
 unsigned long long afb_launch_count(void);
 const char* afb_version(void);

@@ -181,6 +181,38 @@ def main():
     px.close()
     for p in (p_a, p_b, p_s, scratch):
         lib.free(p)
+    # pipelined form: the pushing GEMM in column-chunk order + the chunk-by-chunk local sum and broadcast on a second stream;
+    # identical bits to GEMM + fused exchange, with and without the multicast broadcast, also when the exchange kernel is launched first
+    for multicast in (True, False):
+        px = D.PeerExchange(lib, tdist, rank, world, mp, n, partial_f32=True, multicast=multicast)
+        assert px.ok and px.pipelined_supported(4)
+        p_a, p_b, p_s = lib.to_device(shard_p.a), lib.to_device(shard_p.b), lib.to_device(shard_p.scale)
+        args = lib.make_args(px.partial, p_a, p_b, p_s, mp, n, shard_p.k, flags=pkg.FLAG_C_F32)
+        side = torch.cuda.Stream()
+        outs_p = []
+        for step in range(4):
+            lib.memset(px.c, 0, mp * n * 2)
+            tdist.barrier(); torch.cuda.synchronize()
+            if step == 3:
+                with torch.cuda.stream(side):
+                    px.sub_launches = getattr(px, "sub_launches", 0) + 1      # the exchange kernel reaches the GPU first: it waits for counts the GEMM has yet to make
+                    px.allreduce_pipelined(4, side.cuda_stream)
+                    px.sub_launches -= 1
+                px.gemm_pushing_pipelined(args, 4, stream)
+            else:
+                px.gemm_pushing_pipelined(args, 4, stream)
+                with torch.cuda.stream(side):
+                    px.allreduce_pipelined(4, side.cuda_stream)
+            torch.cuda.synchronize()
+            outs_p.append(lib.to_host(px.c, (mp, n), np.uint16))
+        st = lib.read_status()
+        assert st[0] == 0, f"device status {st}"
+        assert all(np.array_equal(outs[0], o) for o in outs_p), "pipelined exchange differs from GEMM + fused exchange"
+        if rank == 0:
+            print(f"pipelined (multicast address: {'yes' if px.c_multicast else 'no'}): bit-identical to the fused exchange", flush=True)
+        px.close()
+        for p in (p_a, p_b, p_s):
+            lib.free(p)
     # NCCL comparison path
     p32 = torch.empty((m, n), device="cuda", dtype=torch.float32)
     c16 = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)

@@ -299,6 +299,19 @@ def test_host_pointer_entry_point(afb, oracle, m, n, k):
     check_close(oracle, oracle.gemm(case), c, "afb_gemm_host")
 
 
+def test_host_pointer_entry_point_two_calls_in_flight(afb, oracle):
+    """afb_gemm_host_async: three GEMMs queued back to back on alternating staging sets (the third reuses the first one's),
+    one wait at the end; each result against the oracle."""
+    cases = [T.make_case(300, 8192, 128, seed=13), T.make_case(64, 256, 512, seed=14), T.make_case(320, 4096, 256, seed=15)]
+    outs = [np.zeros((c.m, c.n), np.uint16) for c in cases]
+    args = [afb.make_args(o, c.a, c.b, c.scale, c.m, c.n, c.k, ldb=c.ldb) for c, o in zip(cases, outs)]
+    for a in args:
+        afb.gemm_host_async(a)
+    afb.gemm_host_wait()
+    for c, o in zip(cases, outs):
+        check_close(oracle, oracle.gemm(c, threads=4), o, "afb_gemm_host_async")
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("m,n,k,bits,group", [(16, 1000, 4096, 8, 0), (9, 2048, 8192, 4, 128), (16, 136, 1024, 8, 0), (12, 4104, 2048, 4, 0),
                                                (16, 520, 2048, 8, 256), (3, 776, 4096, 4, 128)])
