@@ -75,6 +75,7 @@ int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* ti
 int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s,
                            uint32_t* const* counters = nullptr, uint32_t sub_blocks = 0);
 void prefill_ts_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* m_tiles, uint32_t* n_tiles, uint32_t* arrivals);
+int launch_probe(uint32_t kind, const void* src, size_t bytes, uint32_t ctas, uint32_t smem_bytes, bool pdl, uint32_t* sink, cudaStream_t s);
 int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s);
 
 bool decode_supports(const afb_gemm_args& a);

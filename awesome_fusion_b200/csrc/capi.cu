@@ -439,6 +439,14 @@ int afb_read_status(int32_t out[4]) {
     return AFB_OK;
 }
 
+int afb_probe_launch(uint32_t kind, const void* src, size_t bytes, uint32_t ctas, uint32_t smem_bytes, uint32_t flags, void* stream) {
+    if (kind > 1 || ctas == 0 || ctas > 65535 || smem_bytes > 200 * 1024 || (kind == 1 && (!src || (uintptr_t)src % 16 || bytes % 16))) return AFB_ERR_BAD_ARG;
+    if (flags & ~AFB_FLAG_PDL) return AFB_ERR_BAD_ARG;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    return launch_probe(kind, src, bytes, ctas, smem_bytes, (flags & AFB_FLAG_PDL) != 0, ctx->ar_words + 0 /* never written in practice */, (cudaStream_t)stream);
+}
+
 int afb_phase_timestamps(unsigned long long out[8]) {
     DeviceCtx* ctx = current_ctx();
     if (!ctx) return AFB_ERR_NOT_INIT;

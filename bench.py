@@ -232,6 +232,32 @@ def single_case(lib, torch, name, m, n, k, bits, group, peaks, steps, warmup):
     return res
 
 
+def decode_floor(lib, torch, steps, warmup):
+    """How long a launch of the decode kernel's shape takes when it does nothing, and when it only reads 16.8 MB (the weights of
+    the 4096 x 4096 int8 configuration) -- both as back-to-back launches in a CUDA graph over 24 rotated buffers, without and with
+    programmatic dependent launch.  These are the floors next to which the 4096 x 4096 decode figures have to be read."""
+    import awesome_fusion_b200 as pkg
+    n = k = 4096
+    copies = 24
+    bufs = [torch.randint(-127, 128, (n, k), device="cuda", dtype=torch.int8) for _ in range(copies)]
+    out = {}
+    for kind, kname in ((0, "empty kernel"), (1, "read-only kernel, 16.8 MB")):
+        for ctas, smem in ((256, 52 * 1024), (256, 84 * 1024), (592, 52 * 1024)):
+            for flags, fname in ((0, "plain"), (pkg.FLAG_PDL, "programmatic dependent launch")):
+                def launch_all(stream):
+                    for b in bufs:
+                        lib.probe_launch(kind, b, n * k, ctas, smem, flags, stream)
+                launch_all(torch.cuda.current_stream().cuda_stream)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    launch_all(torch.cuda.current_stream().cuda_stream)
+                us = time_launches(torch, g.replay, steps, warmup) / copies * 1e3
+                out[f"{kname}, {ctas} CTAs x {smem // 1024} KiB, {fname}"] = round(us, 2)
+                del g
+    return out
+
+
 SINGLE_CASES = {
     "decode-m1": (1, 4096, 4096, 8, 0), "decode-m4": (4, 4096, 4096, 8, 0), "decode-m16": (16, 4096, 4096, 8, 0),
     "prefill": (2048, 11008, 4096, 8, 0),
@@ -372,6 +398,9 @@ def run_ours(args):
     stream = torch.cuda.current_stream().cuda_stream
     steps, warm = args.steps, max(3, args.warmup)
 
+    if args.workload == "decode-floor":
+        print(json.dumps({"workload": "decode-floor", "us_per_launch": decode_floor(lib, torch, steps, warm), "status": lib.read_status()}))
+        return 0
     if args.workload != "sharded-mlp":
         m, n, k, bits, group = SINGLE_CASES[args.workload]
         res = single_case(lib, torch, args.workload, m, n, k, bits, group, peaks, steps, warm)
@@ -500,7 +529,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="sharded-mlp", choices=["sharded-mlp"] + sorted(SINGLE_CASES))
+    ap.add_argument("--workload", default="sharded-mlp", choices=["sharded-mlp", "decode-floor"] + sorted(SINGLE_CASES))
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "pipelined", "overlap", "fused", "nccl"])
     ap.add_argument("--no-cases", action="store_true", help="skip the single-GPU case sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")

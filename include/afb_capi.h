@@ -317,6 +317,10 @@ int afb_cast_f32_to_bf16(void* dst_bf16, const void* src_f32, uint32_t rows, uin
 const char* afb_status_string(int status);
 int afb_last_cuda_error(void);             /* cudaError_t of the last failing CUDA call */
 const char* afb_last_cuda_error_string(void);
+/* Launch-floor probes (measurement aid): kind 0 launches a kernel with the given grid (256 threads per CTA) and dynamic shared
+ * memory that does nothing; kind 1 one that only reads `bytes` at `src` with the decode kernel's access pattern.  flags:
+ * AFB_FLAG_PDL or 0.  Timed like the decode kernels they show how much of a few-microsecond GEMM is launch and ramp. */
+int afb_probe_launch(uint32_t kind, const void* src, size_t bytes, uint32_t ctas, uint32_t smem_bytes, uint32_t flags, void* stream);
 /* Phase timestamps of the last row-parallel GEMM + exchange on the current device (measurement aid; written only while the
  * environment variable AFB_PHASE_TIMESTAMPS is set).  Nanoseconds of this GPU's own timer: out[0] GEMM start, [1] GEMM end,
  * [2] exchange kernel start, [3] every rank's GEMM seen complete, [4] sum and broadcast done, [5] every rank's block seen in
