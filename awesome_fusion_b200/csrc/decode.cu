@@ -44,6 +44,7 @@ __host__ __device__ constexpr int ring_bytes(int ring) { return kWarps * ring * 
 __host__ __device__ constexpr int act_bytes(int mt) { return mt == 1 ? 20 * 1024 : 40 * 1024; }
 constexpr int kOffRed = 0;
 __host__ __device__ constexpr int smem_bytes(int mt, int ring) { return ring_bytes(ring) + act_bytes(mt) + 16; }
+constexpr int kSmemMax = 227 * 1024;   // per CTA on sm_100
 static_assert(kRedFloats * 4 <= ring_bytes(4), "the reduction buffer must fit the ring it reuses");
 
 __device__ __forceinline__ void grid_dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -65,7 +66,7 @@ decode_kernel(const DecodeParams p) {
 
     extern __shared__ __align__(16) uint8_t smem[];
     float* s_red = reinterpret_cast<float*>(smem + kOffRed);
-    uint32_t* s_last = reinterpret_cast<uint32_t*>(smem + kOffAct + act_bytes(MT));
+    uint32_t* s_last = reinterpret_cast<uint32_t*>(smem + kOffAct + p.act_bytes);   // the staging area's size is chosen per launch
     const uint32_t s_act = (uint32_t)__cvta_generic_to_shared(smem + kOffAct);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
@@ -275,12 +276,12 @@ cudaError_t launch_one(const DecodeParams& p, dim3 grid, bool pdl, cudaStream_t 
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set.done(dev)) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT, RING));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return e;
         attr_set.mark(dev);
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem_bytes(MT, RING); cfg.stream = s;
+    cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = ring_bytes(RING) + p.act_bytes + 16; cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -297,7 +298,7 @@ int resident_one() {
     int n = cached[dev & 31].load(std::memory_order_acquire);
     if (n == 0) {
         auto kern = decode_kernel<BITS, MT, GROUPED, false, RING>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(MT, RING)) != cudaSuccess) return 0;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax) != cudaSuccess) return 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem_bytes(MT, RING)) != cudaSuccess) return 0;
         cached[dev & 31].store(n, std::memory_order_release);
     }
@@ -338,8 +339,8 @@ bool decode_supports(const afb_gemm_args& a) {
 //   * wr: activations are re-read by every column of CTAs, so more activation rows ask for more channels per CTA
 //     (keeps the activation traffic through L2 below about half of the weight traffic);
 //   * slices: only when the channel dimension alone cannot fill the GPU.
-static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, DecodeParams& p) {
-    const size_t act_cap = (size_t)act_bytes(a.m <= 8 ? 1 : 2);
+// act_cap: bytes of the activation staging area of this launch.
+static void pick_shape(const afb_gemm_args& a, int sm_count, int ctas_per_sm, size_t ws_bytes, size_t counter_count, size_t act_cap, DecodeParams& p) {
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
     const uint32_t sms = (uint32_t)sm_count;
     const uint32_t act_bytes_per_k = 2 * a.m;                      // per k, per column of CTAs
@@ -426,16 +427,51 @@ int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t w
     const int mt = a.m <= 8 ? 1 : 2;
     p.packed = a.b_layout == AFB_LAYOUT_COL_PACKED ? 1u : 0u;
     p.zero = reinterpret_cast<const uint8_t*>(a.ptr_zero);
-    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, p);
+    // Small matrices (one wave of CTAs): the whole K range of a CTA is staged at once when shared memory allows it, so that the
+    // kernel pays the activations' L2 latency once instead of once per pass (16 rows x 4096 k are 128 KiB: one CTA per SM then),
+    // and the ring is 8 deep when that still fits (with AFB_FLAG_PDL it fills while the preceding kernel finishes).  The CTA shape
+    // is the one that fills the most CTA places of the wave; ties go to more resident warps, then to the deeper ring.
+    const uint32_t sms = (uint32_t)ctx->sm_count;
+    const double weight_mb = (double)a.n * a.k * a.b_bits / 8 / 1e6;
+    uint32_t act = (uint32_t)act_bytes(mt);
+    bool deep_ring = false;
+    int forced_wr = 0;
+    static const bool env_single_pass_off = [] { const char* e = getenv("AFB_DECODE_SINGLE_PASS"); return e && atoi(e) == 0; }();
+    if (weight_mb < 48.0 && !env_single_pass_off && !getenv("AFB_DECODE_WR") && !getenv("AFB_DECODE_SLICES")) {
+        const uint32_t chx = a.b_bits == 8 ? 64 : 128;
+        double best_fill = 0.0; uint32_t best_warps = 0, best_need = 0; int best_ring = 0;
+        for (uint32_t wr = 1; wr <= 8; wr *= 2) {
+            const uint32_t ctas = (a.n + 16 * wr - 1) / (16 * wr), per_sm = (ctas + sms - 1) / sms;
+            if (per_sm > 4) continue;
+            const uint32_t round = chx * (kWarps / wr), whole_k = (a.k + round - 1) / round * round;
+            const uint64_t need = (uint64_t)a.m * (whole_k * 2 + 16);   // whole K in whole rounds of the WK warps, no slices
+            if (need > (uint64_t)kSmemMax) continue;
+            for (int ring = 8; ring >= 4; ring -= 4) {
+                if ((uint64_t)(ring_bytes(ring) + need + 16 + 1024) * per_sm > (uint64_t)kSmemMax) continue;
+                const double fill = (double)ctas / ((double)per_sm * sms);
+                const uint32_t warps = per_sm * kWarps;
+                if (fill > best_fill + 1e-9 || (fill > best_fill - 1e-9 && (warps > best_warps || (warps == best_warps && ring > best_ring)))) {
+                    best_fill = fill; best_warps = warps; best_ring = ring; forced_wr = (int)wr; best_need = (uint32_t)need;
+                }
+            }
+        }
+        if (forced_wr) { act = (best_need + 15u) & ~15u; deep_ring = best_ring == 8; }
+    }
+    p.act_bytes = act;
+    pick_shape(a, ctx->sm_count, resident_ctas(a.b_bits, mt, grouped), ws_bytes, counter_count, act, p);
+    if (forced_wr) {   // the single-pass shape: whole K per CTA, no K-slices
+        p.wr = (uint32_t)forced_wr; p.slices = 1; p.kc = a.k; p.streamk = 0;
+        const uint32_t chx = a.b_bits == 8 ? 64 : 128, round = chx * (kWarps / p.wr);
+        p.pass_k = (a.k + round - 1) / round * round;
+    }
     p.ws = ws; p.counters = counters;
     dim3 grid((a.n + 16 * p.wr - 1) / (16 * p.wr), p.slices);
     if (p.streamk) grid = dim3(p.slices, 1);
-    // Deep ring: when a warp owns at most 8 chunks and two CTAs per SM hold the whole grid, all weights of the launch are in
-    // flight at once (small matrices; with AFB_FLAG_PDL they stream in while the preceding kernel finishes).
     const uint32_t ch = a.b_bits == 8 ? 64 : 128;
     const uint32_t chunks_per_warp = (p.kc / ch + (kWarps / p.wr) - 1) / (kWarps / p.wr);
-    bool deep_ring = !p.streamk && chunks_per_warp <= 8 && (uint64_t)grid.x * grid.y <= 2ull * (uint64_t)ctx->sm_count;
+    if (!forced_wr) deep_ring = !p.streamk && chunks_per_warp <= 8 && (uint64_t)grid.x * grid.y <= 2ull * (uint64_t)ctx->sm_count;
     if (const char* e = getenv("AFB_DECODE_DEEP_RING")) deep_ring = atoi(e) != 0 && !p.streamk;   // tuning aid
+    if ((uint64_t)ring_bytes(deep_ring ? 8 : 4) + act + 16 > (uint64_t)kSmemMax) deep_ring = false;
     const bool pdl = (a.flags & AFB_FLAG_PDL) != 0;
     cudaError_t e;
     if (a.b_bits == 8) {

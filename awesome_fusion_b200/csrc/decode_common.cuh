@@ -21,7 +21,8 @@ struct DecodeParams {
     uint32_t packed;  // B is in the pre-packed order of afb_prepack: the unpack yields consecutive k, activations are staged as they lie
     uint32_t wr;      // warps along the channel dimension (1, 2, 4 or 8); WK = 8 / wr
     uint32_t kc;      // k elements per slice (multiple of the chunk)
-    uint32_t pass_k;  // k elements staged per pass (m * (pass_k * 2 + 16) <= the activation buffer)
+    uint32_t pass_k;  // k elements staged per pass (m * (pass_k * 2 + 16) <= act_bytes)
+    uint32_t act_bytes;  // size of the activation staging area in shared memory (chosen per launch)
     uint32_t group_shift;  // log2(group) (groups are powers of two)
     uint32_t slices;  // gridDim.y
     // balanced form (streamk = 1): the grid is one wave of CTAs; the weights are cut into units of 16*wr channels x unit_k

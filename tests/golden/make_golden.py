@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the reference's OWN host code.
 
 Run in a checkout where the reference sources are present:
-    make -C oracle            # builds oracle/_ref/libafb_hostref.so from the reference's headers
+    make -C oracle REF=<reference checkout>/bfAintBGemm     # builds oracle/_ref/libafb_hostref.so from the reference's headers
     python tests/golden/make_golden.py
 The reference has no test vectors of its own (its only check is the opt-in comparison of
 bfAintBGemm.cc:198-214 on time-seeded data), so these files record what its host functions
