@@ -72,7 +72,8 @@ decode_kernel(const DecodeParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const uint32_t wk_count = kWarps / p.wr;
     const uint32_t wr = warp / wk_count, wk = warp % wk_count;
-    const uint32_t xormask = (BITS == 8 && p.enc == AFB_ENC_OFFSET_BINARY) ? 0x80808080u : 0u;
+    // int8: the constant of the sign half of the unpack carries the encoding (dequant.cuh), so offset-binary storage costs no instruction
+    const uint32_t hi8 = p.enc == AFB_ENC_OFFSET_BINARY ? 0xC380C380u : 0xC300C300u;
     const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
     const uint32_t groups_per_row = GROUPED ? (p.k >> p.group_shift) : 0;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * (kRing * kStageBytes) + lane * 16;
@@ -131,12 +132,12 @@ decode_kernel(const DecodeParams p) {
     const uint8_t* src_b = pb + kbyte0 + (size_t)wk * 64;
     const uint32_t src_step = wk_count * 64;
     uint32_t issued = 0;
-    auto issue = [&]() {   // start the copy of this warp's next chunk into ring slot issued % kRing
-        const uint32_t dst = ring + (issued & (kRing - 1)) * kStageBytes;
+    auto issue_to = [&](uint32_t dst) {   // start the copy of this warp's next chunk into the ring slot at dst
         if (ok_a) cp_async16(dst, src_a);
         if (ok_b) cp_async16(dst + 512, src_b);
         src_a += src_step; src_b += src_step; ++issued;
     };
+    auto issue = [&]() { issue_to(ring + (issued & (kRing - 1)) * kStageBytes); };   // ... into ring slot issued % kRing
     const uint16_t* sc_h = reinterpret_cast<const uint16_t*>(p.scale);
     const float* sc_f = reinterpret_cast<const float*>(p.scale);
     const size_t sc_ia = (size_t)(ok_a ? row_a : 0) * groups_per_row, sc_ib = (size_t)(ok_b ? row_b : 0) * groups_per_row;
@@ -195,22 +196,19 @@ decode_kernel(const DecodeParams p) {
 
         const uint32_t chunks_in_pass = plen / CH;
         uint32_t chunk_off = wk * (CH * 2);                 // byte offset of the chunk inside a staged row
-        for (uint32_t cl = wk; cl < chunks_in_pass; cl += wk_count, ++i, chunk_off += wk_count * (CH * 2)) {
-            if (issued < my_chunks) issue();
-            cp_async_commit();
-            if (GROUPED && i + 1 < my_chunks) load_group_scales(sc_a_nxt, sc_b_nxt, z_a_nxt, z_b_nxt, sub_a_nxt, sub_b_nxt);
+        const uint32_t chunk_step = wk_count * (CH * 2);
+        // everything of a chunk after its copy has been issued: activations, weights from ring slot `slot`, unpack, tensor cores
+        auto consume = [&](uint32_t slot, uint32_t coff, uint32_t par) {
             // this lane's activations of the chunk: rows g (and g + 8), k = cl*CH + tig*LK ..
-            const uint32_t par = BITS == 8 ? ((cl & 1u) << 5) : 0u;   // int8: odd chunks have bit 3 of the piece index set
             uint32_t s[MT][AV * 4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int v = 0; v < AV; ++v) {
-                    const uint4 t = lds128(act_base[mt] + chunk_off + (act_off[v] ^ par));
+                    const uint4 t = lds128(act_base[mt] + coff + (act_off[v] ^ par));
                     s[mt][4 * v] = t.x; s[mt][4 * v + 1] = t.y; s[mt][4 * v + 2] = t.z; s[mt][4 * v + 3] = t.w;
                 }
-            cp_async_wait<kRing - 1>();   // this warp's chunk i has landed (each lane reads only what it copied itself)
-            const uint32_t slot = ring + (i & (kRing - 1)) * kStageBytes;
+            cp_async_wait<kRing - 1>();   // this warp's chunk has landed (each lane reads only what it copied itself)
             const uint4 wa4 = lds128(slot), wb4 = lds128(slot + 512);
             const uint32_t wav[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
             const uint32_t wbv[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
@@ -223,8 +221,8 @@ decode_kernel(const DecodeParams p) {
             for (int j = 0; j < 4; ++j) {
                 if (BITS == 8) {
                     uint32_t a0, a1, a2, a3;
-                    s8x4_to_bf16_strided(wav[j] ^ xormask, a0, a2);
-                    s8x4_to_bf16_strided(wbv[j] ^ xormask, a1, a3);
+                    s8x4_enc_to_bf16_strided(wav[j], hi8, a0, a2);
+                    s8x4_enc_to_bf16_strided(wbv[j], hi8, a1, a3);
                     if (ZP) { a0 = bf16x2_sub(a0, z_a); a2 = bf16x2_sub(a2, z_a); a1 = bf16x2_sub(a1, z_b); a3 = bf16x2_sub(a3, z_b); }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
@@ -248,6 +246,30 @@ decode_kernel(const DecodeParams p) {
                 }
                 sc_a = sc_a_nxt; sc_b = sc_b_nxt;
                 z_a = z_a_nxt; z_b = z_b_nxt; sub_a = sub_a_nxt; sub_b = sub_b_nxt;
+            }
+        };
+        uint32_t cl = wk;
+        while (cl < chunks_in_pass) {
+            if ((i & (kRing - 1)) == 0 && cl + (kRing - 1) * wk_count < chunks_in_pass) {
+                // a whole turn of the ring, unrolled: ring slots are compile-time offsets and the copy issued while chunk i + u is
+                // consumed goes to slot (u - 1) mod kRing (the issue cursor runs kRing - 1 chunks ahead until the chunks run out)
+                const uint32_t par0 = BITS == 8 ? ((cl & 1u) << 5) : 0u;                      // int8: odd chunks have bit 3 of the piece index set
+                const uint32_t par1 = BITS == 8 ? par0 ^ ((wk_count & 1u) << 5) : 0u;          // parity of cl + wk_count
+#pragma unroll
+                for (int u = 0; u < kRing; ++u) {
+                    if (issued < my_chunks) issue_to(ring + ((u + kRing - 1) & (kRing - 1)) * kStageBytes);
+                    cp_async_commit();
+                    if (GROUPED && i + 1 < my_chunks) load_group_scales(sc_a_nxt, sc_b_nxt, z_a_nxt, z_b_nxt, sub_a_nxt, sub_b_nxt);
+                    consume(ring + u * kStageBytes, chunk_off, (u & 1) ? par1 : par0);
+                    ++i; chunk_off += chunk_step;
+                }
+                cl += kRing * wk_count;
+            } else {
+                if (issued < my_chunks) issue();
+                cp_async_commit();
+                if (GROUPED && i + 1 < my_chunks) load_group_scales(sc_a_nxt, sc_b_nxt, z_a_nxt, z_b_nxt, sub_a_nxt, sub_b_nxt);
+                consume(ring + (i & (kRing - 1)) * kStageBytes, chunk_off, BITS == 8 ? ((cl & 1u) << 5) : 0u);
+                ++i; chunk_off += chunk_step; cl += wk_count;
             }
         }
     }

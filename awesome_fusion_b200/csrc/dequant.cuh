@@ -73,6 +73,17 @@ __device__ __forceinline__ void s8x4_to_bf16_strided(uint32_t w, uint32_t& p02, 
     p13 = s8pair_to_bf16x2(w >> 8);
 }
 
+// The same for either storage encoding without a separate flip: `hi` = 0xC300C300 (two's complement) or 0xC380C380 (value + 128).
+// With value + 128 the top bit is inverted, so the sign half is -256 + 128 * bit7 = the bf16 pattern 0xC380 with bit 7 toggled off.
+__device__ __forceinline__ uint32_t s8pair_enc_to_bf16x2(uint32_t x, uint32_t hi) {
+    const uint32_t lo = lop3_and_or(x, 0x007f007fu, 0x43004300u);   // 128 + (v & 0x7f)
+    return bf16x2_add(lo, lop3_and_xor(x, 0x00800080u, hi));         // two's complement: -128 - 128 * bit7; offset: -256 + 128 * bit7
+}
+__device__ __forceinline__ void s8x4_enc_to_bf16_strided(uint32_t w, uint32_t hi, uint32_t& p02, uint32_t& p13) {
+    p02 = s8pair_enc_to_bf16x2(w, hi);
+    p13 = s8pair_enc_to_bf16x2(w >> 8, hi);
+}
+
 // magic = 0x43084308 for two's-complement nibbles, 0x43004300 for offset-binary (+8) nibbles.
 // x holds two nibbles in bits [0,4) and [16,20) (other bits ignored) -> two exact bf16.
 // `sub` is the packed-bf16 constant that is subtracted: 136 without zero-points, 136 + zero with them (the same instruction).
