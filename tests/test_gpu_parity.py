@@ -16,7 +16,7 @@ TOL = 1e-2            # max relative error on bf16 outputs
 FLOOR_FRAC = 0.05     # |ref| below this fraction of RMS(ref) is compared against the floor instead
 # Group-scaled prefill in its default (one rounded bf16 term per weight) mode against the pure-fp32 formula, at the same floor:
 # the documented exception to the 1e-2 contract (AFB_FLAG_GROUP_EXACT is the mode that meets it).
-GROUPED_ONE_TERM_BOUND = 0.25
+GROUPED_ONE_TERM_BOUND = 0.25    # measured: 0.11 to 0.16 of max(|ref|, 0.05 x RMS), NRMS 1.6e-3
 
 
 def check_close(oracle, ref, got_bf16, what, tol=TOL, floor_frac=FLOOR_FRAC):
@@ -407,3 +407,51 @@ def test_prefill_tail_tiles_split_along_k(afb, oracle, monkeypatch, bits, group,
     # the split only changes the order of the fp32 additions of the two tail tiles: everything else is bit-identical
     same = np.mean(a == whole)
     assert same > 0.97, same
+
+
+@pytest.mark.gpu
+def test_measurement_aids_do_not_disturb_the_device(afb, oracle):
+    """afb_probe_launch (empty and read-only kernels with a decode-like launch shape, with and without programmatic dependent
+    launch) and afb_phase_timestamps answer with a status, and a GEMM right after them is still correct."""
+    buf = afb.malloc(1 << 20)
+    afb.memset(buf, 1, 1 << 20)
+    for kind in (0, 1):
+        for flags in (0, pkg.FLAG_PDL):
+            afb.probe_launch(kind, buf, 1 << 20, 64, 52 * 1024, flags)
+    afb.device_sync()
+    assert afb.lib.afb_probe_launch(2, buf, 1 << 20, 64, 0, 0, None) == -1
+    assert len(afb.phase_timestamps()) == 8
+    afb.free(buf)
+    case = T.make_case(3, 256, 512, seed=5)
+    for flags in (0, pkg.FLAG_PDL):
+        out, _ = T.run_case(afb, case, flags=flags)
+        check_close(oracle, oracle.gemm(case), out, "GEMM after the probes")
+    assert afb.read_status()[0] == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k,bits,group", [(1, 4096, 4096, 8, 0), (8, 4096, 4096, 8, 0), (16, 4096, 4096, 8, 0), (16, 2048, 4096, 4, 128), (12, 1000, 2048, 8, 0),
+                                               (16, 4096, 4096 + 64, 8, 0), (5, 520, 8192, 4, 0)])
+def test_decode_back_to_back_with_dependent_launch(afb, oracle, m, n, k, bits, group):
+    """Several decode GEMMs on rotating weight buffers queued back to back with AFB_FLAG_PDL (each may start while its
+    predecessor still runs): every result against the oracle, and identical to the same launch without the flag.  The shapes
+    include the small-matrix forms (8-stage ring, whole K staged in one pass)."""
+    cases = [T.make_case(m, n, k, bits=bits, group=group, seed=200 + i, scale_range=(0.005, 0.05)) for i in range(3)]
+    dcs = [T.DeviceCase(afb, c) for c in cases]
+    try:
+        for _ in range(2):
+            for dc in dcs:
+                afb.gemm_launch(dc.args(variant=pkg.VARIANT_DECODE, flags=pkg.FLAG_PDL))
+        afb.device_sync()
+        with_flag = [dc.result()[0] for dc in dcs]
+        for dc in dcs:
+            afb.gemm_launch(dc.args(variant=pkg.VARIANT_DECODE))
+            afb.device_sync()
+        plain = [dc.result()[0] for dc in dcs]
+    finally:
+        for dc in dcs:
+            dc.close()
+    for c, a, b in zip(cases, with_flag, plain):
+        assert np.array_equal(a, b)
+        check_close(oracle, oracle.gemm(c, threads=4), a, f"decode with dependent launch {m}x{n}x{k}")
+    assert afb.read_status()[0] == 0
