@@ -176,8 +176,10 @@ decode_kernel(const DecodeParams p) {
         if (pk != ks) __syncthreads();   // the previous pass has been consumed by every warp
         {   // stage the activations of [pk, pk + plen), permuted into the pairing the weights unpack to
             const uint32_t pieces = plen >> 3;
-            for (uint32_t r = tid >> 6; r < p.m; r += 4)
-                for (uint32_t pc = tid & 63; pc < pieces; pc += 64) {
+            // all 256 threads take part whatever m is: 256, 128 or 64 threads per row
+            const uint32_t rsh = p.m >= 4 ? 6u : (p.m >= 2 ? 7u : 8u), per_row = 1u << rsh, rstep = 256u >> rsh;
+            for (uint32_t r = tid >> rsh; r < p.m; r += rstep)
+                for (uint32_t pc = tid & (per_row - 1); pc < pieces; pc += per_row) {
                     const uint4 v = ldg_act(p.a + (size_t)r * p.lda + pk + pc * 8);
                     uint4 o;
                     if (p.packed) {   // pre-packed weights unpack to consecutive k: the activations are used as they lie

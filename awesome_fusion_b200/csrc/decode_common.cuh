@@ -70,7 +70,8 @@ template <bool GROUPED, typename CtaOf>
 __device__ __forceinline__ void decode_finish(const DecodeParams& p, const float* s_red, uint32_t* s_last, uint32_t cb, uint32_t nblk,
                                               uint32_t wk_count, uint32_t mcols, CtaOf cta_of) {
     const uint32_t tid = threadIdx.x;
-    const uint32_t rows_cta = 16 * p.wr;
+    const uint32_t rows_cta = 16 * p.wr;                // a power of two: 16, 32, 64 or 128
+    const uint32_t rows_shift = 31u - (uint32_t)__clz(rows_cta);
     const uint32_t outputs = rows_cta * mcols;          // <= 2048
     uint32_t contributors = p.slices, my_slot = blockIdx.y;
     if (p.streamk) {   // the CTAs whose runs of units touch this channel block, in CTA order (= ascending K)
@@ -79,7 +80,7 @@ __device__ __forceinline__ void decode_finish(const DecodeParams& p, const float
     }
     const bool single = contributors == 1;
     for (uint32_t idx = tid; idx < outputs; idx += kThreads) {
-        const uint32_t mm = idx / rows_cta, r = idx - mm * rows_cta;   // consecutive threads -> consecutive channels
+        const uint32_t mm = idx >> rows_shift, r = idx & (rows_cta - 1);   // consecutive threads -> consecutive channels
         const uint32_t nn = nblk + r;
         if (mm >= p.m || nn >= p.n) continue;
         const uint32_t w0 = (r >> 4) * wk_count;
@@ -103,7 +104,7 @@ __device__ __forceinline__ void decode_finish(const DecodeParams& p, const float
         if (*s_last) {
             __threadfence();
             for (uint32_t idx = tid; idx < p.m * rows_cta; idx += kThreads) {
-                const uint32_t mm = idx / rows_cta, nn = nblk + (idx % rows_cta);
+                const uint32_t mm = idx >> rows_shift, nn = nblk + (idx & (rows_cta - 1));
                 if (nn >= p.n) continue;
                 const float* src = p.ws + (size_t)mm * p.n + nn;
                 const size_t slice_stride = (size_t)p.m * p.n;
