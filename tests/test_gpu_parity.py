@@ -365,6 +365,10 @@ def test_exchange_wait_runs_out_and_reports_status(afb, oracle):
         st = afb.read_status()                            # synchronises
         assert st[0] == -4 and st[1] == 10 and st[2] == 0 and st[3] == 1, st      # AFB_ERR_TIMEOUT, phase-0 wait, rank 0, epoch 1
         assert np.all(afb.to_host(c, (m * n * 2,), np.uint8) == 0xCD)             # nothing was stored
+        # ... and completion was not announced: every CTA runs its own clock, and one that gave up vetoes the "my block is in
+        # place" signal (second half of the signal words) even if the last CTA to finish saw the peers in time
+        assert np.all(afb.to_host(peer_sig, (2 * D.MAX_RANKS,), np.uint32)[D.MAX_RANKS:] == 0)
+        assert np.all(afb.to_host(sig, (2 * D.MAX_RANKS,), np.uint32)[D.MAX_RANKS:] == 0)
         assert afb.read_status()[0] == 0                                          # reading cleared it
         # the context is intact: an ordinary GEMM still runs and is right
         case = T.make_case(4, 256, 512, seed=82)

@@ -56,6 +56,23 @@ def test_validation_without_gpu(lib):
     assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
     bad = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256, group=96)
     assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    # pointers the kernels would load or store through as 2- or 4-byte words must be aligned to them: a status, never a GPU fault
+    bad = lib.make_args(0x1000, 0x1000, 0x1000, 0x1002, 4, 128, 256)                                  # fp32 scales at a 2-byte boundary
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    bad = lib.make_args(0x1000, 0x1000, 0x1000, 0x1001, 4, 128, 256, scale_dtype=pkg.SCALE_BF16)      # bf16 scales at an odd address
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    bad = lib.make_args(0x1001, 0x1000, 0x1000, 0x1000, 4, 128, 256)                                  # bf16 C at an odd address
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(bad), ctypes.byref(v)) == -1
+    assert lib.gemm_launch_static_status(lib.make_args(0x1000, 0x1000, 0x1000, 0x1002, 4, 128, 256)) == -1
+    ok = lib.make_args(0x1000, 0x1000, 0x1000, 0x1002, 4, 128, 256, scale_dtype=pkg.SCALE_BF16)       # bf16 scales at a 2-byte boundary are fine
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(ok), ctypes.byref(v)) == 0
+    # packed layout, flags and the tail of the argument block
+    pk = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256, layout=pkg.LAYOUT_COL_PACKED, flags=pkg.FLAG_PDL)
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(pk), ctypes.byref(v)) == 0 and v.value == pkg.VARIANT_DECODE
+    pk.reserved2 = 1
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(pk), ctypes.byref(v)) == -1
+    g32 = lib.make_args(0x1000, 0x1000, 0x1000, 0x1000, 4, 128, 256, bits=4, group=32, scale_dtype=pkg.SCALE_BF16)   # groups of 32: the prefill kernel takes them
+    assert lib.lib.afb_gemm_resolve_variant(ctypes.byref(g32), ctypes.byref(v)) == 0 and v.value == pkg.VARIANT_PREFILL
     assert lib.lib.afb_status_string(-4).decode().startswith("a bounded")
 
 

@@ -73,3 +73,8 @@ def test_decode_graph_replay_equals_direct_call():
     torch.cuda.synchronize()
     assert torch.equal(first.view(torch.int16), direct.view(torch.int16))
     assert torch.equal(second.view(torch.int16), want2.view(torch.int16))
+    # the same with programmatic dependent launch inside the graph (weights declared constant): identical bits
+    gp = torch_op.DecodeGraph(a2, b, s, bits=4, group_size=128, weights_constant=True)
+    third = gp.replay().clone()
+    torch.cuda.synchronize()
+    assert torch.equal(third.view(torch.int16), want2.view(torch.int16))
