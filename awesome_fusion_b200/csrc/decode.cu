@@ -50,13 +50,17 @@ static_assert(kRedFloats * 4 <= ring_bytes(4), "the reduction buffer must fit th
 __device__ __forceinline__ void grid_dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+__host__ __device__ constexpr int min_ctas_per_sm(int bits, int mt, bool grouped, int ring) {
+    return ring == 8 ? 2 : ((bits == 4 && grouped) ? (mt == 1 ? 3 : 2) : (mt == 1 ? AFB_DECODE_MT1_CTAS : AFB_DECODE_MT2_CTAS));
+}
+
 // ZP (int8 only): zero-points cost one more packed subtraction per pair of weights; int4 zero-points ride on the constant the
 // unpack subtracts anyway, so those instances take them without a switch.
 template <int BITS, int MT, bool GROUPED, bool ZP, int RING>
 // resident CTAs per SM the register budget is cut for: the group-scaled int4 kernels want more registers than the others (16 rows:
 // about 118, 12 % faster with two CTAs and no spills than with three squeezed into 80; 8 rows: 80, 3 to 8 % faster with three
 // CTAs than with four at 64); the other kernels gain nothing or lose (measured)
-__global__ void __launch_bounds__(kThreads, RING == 8 ? 2 : ((BITS == 4 && GROUPED) ? (MT == 1 ? 3 : 2) : (MT == 1 ? AFB_DECODE_MT1_CTAS : AFB_DECODE_MT2_CTAS)))
+__global__ void __launch_bounds__(kThreads, min_ctas_per_sm(BITS, MT, GROUPED, RING))
 decode_kernel(const DecodeParams p) {
     constexpr int kRing = RING;
     constexpr int kOffAct = ring_bytes(RING);
@@ -178,21 +182,48 @@ decode_kernel(const DecodeParams p) {
             const uint32_t pieces = plen >> 3;
             // all 256 threads take part whatever m is: 256, 128 or 64 threads per row
             const uint32_t rsh = p.m >= 4 ? 6u : (p.m >= 2 ? 7u : 8u), per_row = 1u << rsh, rstep = 256u >> rsh;
-            for (uint32_t r = tid >> rsh; r < p.m; r += rstep)
-                for (uint32_t pc = tid & (per_row - 1); pc < pieces; pc += per_row) {
-                    const uint4 v = ldg_act(p.a + (size_t)r * p.lda + pk + pc * 8);
-                    uint4 o;
-                    if (p.packed) {   // pre-packed weights unpack to consecutive k: the activations are used as they lie
-                        o = v;
-                    } else if (BITS == 8) {  // {k0,k2},{k1,k3},{k4,k6},{k5,k7}
-                        o.x = prmt(v.x, v.y, 0x5410u); o.y = prmt(v.x, v.y, 0x7632u);
-                        o.z = prmt(v.z, v.w, 0x5410u); o.w = prmt(v.z, v.w, 0x7632u);
-                    } else {          // {k0,k4},{k1,k5},{k2,k6},{k3,k7}
-                        o.x = prmt(v.x, v.z, 0x5410u); o.y = prmt(v.x, v.z, 0x7632u);
-                        o.z = prmt(v.y, v.w, 0x5410u); o.w = prmt(v.y, v.w, 0x7632u);
-                    }
-                    *reinterpret_cast<uint4*>(smem + kOffAct + r * act_row_bytes + swz_piece(pc) * 16) = o;
+            auto put = [&](uint32_t r, uint32_t pc, const uint4& v) {
+                uint4 o;
+                if (p.packed) {   // pre-packed weights unpack to consecutive k: the activations are used as they lie
+                    o = v;
+                } else if (BITS == 8) {  // {k0,k2},{k1,k3},{k4,k6},{k5,k7}
+                    o.x = prmt(v.x, v.y, 0x5410u); o.y = prmt(v.x, v.y, 0x7632u);
+                    o.z = prmt(v.z, v.w, 0x5410u); o.w = prmt(v.z, v.w, 0x7632u);
+                } else {          // {k0,k4},{k1,k5},{k2,k6},{k3,k7}
+                    o.x = prmt(v.x, v.z, 0x5410u); o.y = prmt(v.x, v.z, 0x7632u);
+                    o.z = prmt(v.y, v.w, 0x5410u); o.w = prmt(v.y, v.w, 0x7632u);
                 }
+                *reinterpret_cast<uint4*>(smem + kOffAct + r * act_row_bytes + swz_piece(pc) * 16) = o;
+            };
+            if constexpr (min_ctas_per_sm(BITS, MT, GROUPED, RING) <= 2) {
+                // The instances with 128 registers per thread send their loads out in batches of 8, across row boundaries, before
+                // any of them is used: a pass then costs (pieces per thread / 8) trips to L2, and with the whole K range staged at
+                // once those trips are most of what the kernel waits for before its first tensor-core instruction (4096 x 4096,
+                // 16 rows: 9.8 us instead of 12.7).  The instances with tighter register budgets lose 3 to 7 % with it (measured).
+                constexpr int kStageBatch = 8;
+                const uint32_t pc_first = tid & (per_row - 1);
+                uint32_t r = tid >> rsh, pc = pc_first;
+                while (r < p.m) {
+                    uint4 v[kStageBatch];
+                    uint32_t r2 = r, pc2 = pc;   // the second loop walks the same (row, piece) sequence again
+#pragma unroll
+                    for (int b = 0; b < kStageBatch; ++b) {
+                        if (r < p.m && pc < pieces) v[b] = ldg_act(p.a + (size_t)r * p.lda + pk + pc * 8);
+                        pc += per_row;
+                        if (pc >= pieces) { pc = pc_first; r += rstep; }
+                    }
+#pragma unroll
+                    for (int b = 0; b < kStageBatch; ++b) {
+                        if (r2 < p.m && pc2 < pieces) put(r2, pc2, v[b]);
+                        pc2 += per_row;
+                        if (pc2 >= pieces) { pc2 = pc_first; r2 += rstep; }
+                    }
+                }
+            } else {
+                for (uint32_t r = tid >> rsh; r < p.m; r += rstep)
+                    for (uint32_t pc = tid & (per_row - 1); pc < pieces; pc += per_row)
+                        put(r, pc, ldg_act(p.a + (size_t)r * p.lda + pk + pc * 8));
+            }
         }
         __syncthreads();
 

@@ -133,10 +133,6 @@ __global__ void __launch_bounds__(kThreadsFwd, 1)
 prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w, const TsParams p) {
     using L = TsLayout<BITS, BMA>;
     constexpr int S = L::kStages;
-    // tiles of 128 activation rows: the two converter warps of a lane quarter take alternate K steps (see the converter section)
-    constexpr bool kAlt = BMA == 128;
-    constexpr uint32_t kConvArrivals = kAlt ? kWorkerWarps / 2 : kWorkerWarps;   // converter warps that work on one K step
-    static_assert(!kAlt || ((S & (S - 1)) == 0 && (kSlotsA & (kSlotsA - 1)) == 0), "the alternating form computes ring positions from the step number");
     extern __shared__ uint8_t smem_raw_base[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw_base) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw_base + (smem_base - ptx::smem_u32(smem_raw_base));
@@ -177,8 +173,8 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
 
     if (threadIdx.x == 0) {
         if (p.ts && blockIdx.x == 0) p.ts[0] = ptx::globaltimer();
-        for (int s = 0; s < S; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty_act(s), 1); ptx::mbar_init(bar_empty_raw(s), kConvArrivals); }
-        for (int s = 0; s < kSlotsA; ++s) { ptx::mbar_init(bar_full_a(s), kConvArrivals); ptx::mbar_init(bar_empty_a(s), 1); }
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty_act(s), 1); ptx::mbar_init(bar_empty_raw(s), kWorkerWarps); }
+        for (int s = 0; s < kSlotsA; ++s) { ptx::mbar_init(bar_full_a(s), kWorkerWarps); ptx::mbar_init(bar_empty_a(s), 1); }
         ptx::mbar_init(bar_acc_full, 1);
         ptx::mbar_init(bar_acc_empty, kWorkerWarps);
         ptx::mbar_init(bar_tile_stored, kWorkerWarps);
@@ -290,18 +286,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             raw_off[i] = BITS == 8 ? ch * 64 + ((piece ^ ((ch >> 1) & 3)) << 4) + (byte & 15)
                                    : ch * 32 + ((piece ^ ((ch >> 2) & 1)) << 4) + (byte & 15);
         }
-        uint32_t raw_off_alt[2][kPieces];   // alternating form: both 32-wide halves of the step
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < kPieces; ++i) {
-                const uint32_t byte = h * kRawPer + i * 16;
-                const uint32_t piece = byte >> 4;
-                raw_off_alt[h][i] = BITS == 8 ? ch * 64 + ((piece ^ ((ch >> 1) & 3)) << 4) + (byte & 15)
-                                              : ch * 32 + ((piece ^ ((ch >> 2) & 1)) << 4) + (byte & 15);
-            }
         uint32_t st = 0, ph = 0, sa = 0, pa = 0, it = 0;
-        uint32_t alt_g = 0;                 // alternating form: K steps this CTA has gone through so far
         bool ok = true;
         Item w;
         for (; ok && get_item(it, w); ++it) {
@@ -310,92 +295,6 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
             tile_coords(p, t, mt_, nt_);
             const uint32_t m0 = mt_ * BMA, n0 = nt_ * BNW;
             const uint32_t nn = n0 + ch;
-            if constexpr (kAlt) {
-            // Alternating form (tiles of 128 activation rows: little tensor-core work per converted weight, so the pace is set by
-            // the latency of one conversion step -- barrier, shared-memory read, unpack, tensor-memory store -- not by throughput).
-            // The two warps of a lane quarter take ALTERNATE K steps instead of the two halves of every step: a thread converts
-            // all 64 k of its row in its own steps, in two halves through the same registers, and two steps are in flight per SM.
-            const uint32_t spk = (GROUPED && p.exact) ? 2u : 1u;   // tensor-memory slots per K step
-            auto load_half = [&](uint32_t kpos, uint32_t& sc, uint32_t& zb) {
-                sc = 0; zb = 0;
-                if (!GROUPED) return;
-                const uint32_t gidx = kpos / p.group;
-                if (nn >= p.n || gidx >= groups_per_row) return;
-                sc = bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
-                if (has_zero) zb = p.zero[(size_t)nn * groups_per_row + gidx];
-            };
-            uint32_t sc_n[2] = {0, 0}, zb_n[2] = {0, 0};
-            uint32_t kb = w.kb0 + ((alt_g ^ kq) & 1u);              // this warp's steps are those whose running number has its parity
-            if (GROUPED && kb < w.kb1) { load_half(kb * BK, sc_n[0], zb_n[0]); load_half(kb * BK + 32, sc_n[1], zb_n[1]); }
-            const uint32_t zb_chan = (!GROUPED && has_zero && nn < p.n) ? p.zero[nn] : 0u;
-            for (; kb < w.kb1; kb += 2) {
-                const uint32_t g = alt_g + (kb - w.kb0);
-                const uint32_t st_ = g & (uint32_t)(S - 1), ph_ = (g / (uint32_t)S) & 1u;
-                const uint32_t sa_ = (g * spk) & (uint32_t)(kSlotsA - 1), pa_ = ((g * spk) / (uint32_t)kSlotsA) & 1u;
-                uint32_t sc_h[2] = {sc_n[0], sc_n[1]}, zb_h[2] = {GROUPED ? zb_n[0] : zb_chan, GROUPED ? zb_n[1] : zb_chan};
-                if (GROUPED && kb + 2 < w.kb1) { load_half((kb + 2) * BK, sc_n[0], zb_n[0]); load_half((kb + 2) * BK + 32, sc_n[1], zb_n[1]); }
-                const bool two_terms = spk == 2u;
-                if (!wait_or_abort(bar_full(st_), ph_, abort_flag) || !wait_or_abort(bar_empty_a(sa_), pa_ ^ 1u, abort_flag) ||
-                    (two_terms && !wait_or_abort(bar_empty_a(sa_ + 1), pa_ ^ 1u, abort_flag))) {
-                    if (!*abort_flag) { report_timeout(p.status, 24, (int)t, (int)kb); *abort_flag = 1; }
-                    ok = false; break;
-                }
-                ptx::tc_fence_after_sync();
-                const uint8_t* raw = smem_gen + L::kOffRaw + st_ * L::kRawBytes;
-                constexpr int kWords = kRawPer / 4, kOut = kKPer / 2;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t w[kWords], o[kOut];
-                    if (kRawPer >= 16) {
-#pragma unroll
-                        for (int i = 0; i < kPieces; ++i) {
-                            const uint4 v = *reinterpret_cast<const uint4*>(raw + raw_off_alt[h][i]);
-                            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-                        }
-                    } else {
-                        const uint2 v = *reinterpret_cast<const uint2*>(raw + raw_off_alt[h][0]);
-                        w[0] = v.x; w[1] = v.y;
-                    }
-                    const uint32_t z8h = has_zero ? zero8_const(zb_h[h], p.enc) : 0u;
-                    const uint32_t sub4h = has_zero ? zero4_const(zb_h[h], p.enc) : 0x43084308u;
-#pragma unroll
-                    for (int j = 0; j < kWords; ++j) {
-                        if (BITS == 8) {
-                            s8x4_to_bf16_pairs(w[j] ^ xormask, packed, o[2 * j], o[2 * j + 1]);
-                            if (has_zero) { o[2 * j] = bf16x2_sub(o[2 * j], z8h); o[2 * j + 1] = bf16x2_sub(o[2 * j + 1], z8h); }
-                        } else {
-                            uint32_t qv[4];
-                            s4x8_to_bf16_pairs(w[j], magic4, packed, qv, sub4h);
-                            o[4 * j] = qv[0]; o[4 * j + 1] = qv[1]; o[4 * j + 2] = qv[2]; o[4 * j + 3] = qv[3];
-                        }
-                    }
-                    const uint32_t taddr = tmem_base + ((q * 32u) << 16) + L::kColA + sa_ * 32 + h * kOut;
-                    if (two_terms) {
-                        uint32_t lo[kOut];
-#pragma unroll
-                        for (int j = 0; j < kOut; ++j) {
-                            const uint32_t hi = bf16x2_mul(o[j], sc_h[h]);
-                            lo[j] = bf16x2_fma(o[j], sc_h[h], hi ^ 0x80008000u);
-                            o[j] = hi;
-                        }
-                        ptx::tmem_st_cols(taddr + 32, lo);
-                    } else if (GROUPED) {
-#pragma unroll
-                        for (int j = 0; j < kOut; ++j) o[j] = bf16x2_mul(o[j], sc_h[h]);
-                    }
-                    ptx::tmem_st_cols(taddr, o);
-                }
-                ptx::tmem_st_wait();
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(bar_full_a(sa_));
-                    if (two_terms) ptx::mbar_arrive(bar_full_a(sa_ + 1));
-                    ptx::mbar_arrive(bar_empty_raw(st_));
-                }
-            }
-            alt_g += w.kb1 - w.kb0;
-            } else {
             // Scale (and zero-point) of the group this thread's kKPer consecutive k of the step lie in (groups are multiples of kKPer,
             // so a thread never straddles one).  The next group's values are fetched one group ahead.
             uint32_t sc_cur = 0, sc_nxt = 0, zb_cur = 0, zb_nxt = 0;
@@ -481,7 +380,6 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 if (++st == S) { st = 0; ph ^= 1u; }
                 sa += two_terms ? 2 : 1;
                 if (sa == kSlotsA) { sa = 0; pa ^= 1u; }
-            }
             }
             if (!ok) break;
             // ---- epilogue of this tile: the accumulator is complete once the last MMA has been committed ----
