@@ -196,11 +196,13 @@ decode_kernel(const DecodeParams p) {
                 *reinterpret_cast<uint4*>(smem + kOffAct + r * act_row_bytes + swz_piece(pc) * 16) = o;
             };
             if constexpr (min_ctas_per_sm(BITS, MT, GROUPED, RING) <= 2) {
-                // The instances with 128 registers per thread send their loads out in batches of 8, across row boundaries, before
-                // any of them is used: a pass then costs (pieces per thread / 8) trips to L2, and with the whole K range staged at
-                // once those trips are most of what the kernel waits for before its first tensor-core instruction (4096 x 4096,
-                // 16 rows: 9.8 us instead of 12.7).  The instances with tighter register budgets lose 3 to 7 % with it (measured).
-                constexpr int kStageBatch = 8;
+                // The instances with 128 registers per thread send their loads out in batches (8 with the 8-stage ring, 4 with the
+                // 4-stage ring), across row boundaries, before any of them is used: a pass then costs (pieces per thread / batch)
+                // trips to L2, and with the whole K range staged at once those trips are most of what the kernel waits for before
+                // its first tensor-core instruction (4096 x 4096, 16 rows: 9.8 us instead of 12.7; 28672 x 8192 int4 group-128,
+                // 16 rows, batches of 4: 62 us instead of 68, batches of 8: 70).  The instances with tighter register budgets
+                // lose 3 to 7 % with it (measured).
+                constexpr int kStageBatch = RING == 8 ? 8 : 4;
                 const uint32_t pc_first = tid & (per_row - 1);
                 uint32_t r = tid >> rsh, pc = pc_first;
                 while (r < p.m) {

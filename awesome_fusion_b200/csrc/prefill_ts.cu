@@ -46,6 +46,7 @@ struct TsParams {
     uint32_t m_rot;        // row tiles are taken in rotated order, starting at this one (spreads the peers a rank pushes to)
     uint32_t group_m;      // tile order: groups of group_m row tiles; inside a group the channel tiles advance, row tile fastest
     uint32_t c_f32;
+    uint32_t c_tma;        // bf16 C goes out as tile stores through shared memory (tmap_c is valid): plain GEMM, no fusion, no exchange
     uint32_t packed;       // B is in the pre-packed order of afb_prepack: the cheap unpack yields consecutive k
     uint32_t exact;        // group scales only: the weight q * s goes to the tensor cores as TWO bf16 terms, hi = bf16_rn(q * s) and
                            // lo = q * s - hi (exact: the product has at most 16 significant bits), in two TMEM slots and two MMAs
@@ -88,7 +89,10 @@ struct TsLayout {
     static constexpr int kOffBars = kOffRaw + kStages * kRawBytes;
     static constexpr int kNumBars = 3 * kStages + 2 * kSlotsA + 6;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
-    static constexpr int kDynamic = kOffMisc + 16 + 1024;
+    // epilogue staging: one [32 activation rows][32 channels] bf16 block (2 KiB) per converter warp, the source of a tile store
+    static constexpr int kStageOutBytes = 32 * 32 * 2;
+    static constexpr int kOffOut = (kOffMisc + 16 + 127) / 128 * 128;
+    static constexpr int kDynamic = kOffOut + kWorkerWarps * kStageOutBytes + 1024;
     static constexpr uint32_t kTmemCols = 512;                   // accumulator [0, BMA) + weight slots [256, 256 + kSlotsA * 32)
     static constexpr uint32_t kColA = 256;
 };
@@ -130,7 +134,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 
 template <int BITS, bool GROUPED, int BMA>
 __global__ void __launch_bounds__(kThreadsFwd, 1)
-prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w, const TsParams p) {
+prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w,
+                  const __grid_constant__ CUtensorMap tmap_c, const TsParams p) {
     using L = TsLayout<BITS, BMA>;
     constexpr int S = L::kStages;
     extern __shared__ uint8_t smem_raw_base[];
@@ -185,6 +190,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmap_act);
         ptx::prefetch_tmap(&tmap_w);
+        if (p.c_tma) ptx::prefetch_tmap(&tmap_c);
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), L::kTmemCols);
@@ -429,6 +435,23 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                             p.c[(size_t)(mrow + j) * p.ldc + nout] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
                         }
                     }
+                } else if (p.c_tma) {
+                    // bf16 result through shared memory: lane = channel writes its 32 rows into a [row][channel] block (64 contiguous
+                    // bytes per warp instruction, no bank conflicts), one lane hands the block to the copy engine as a 32 x 32 tile
+                    // store (clipped at the edges of C), and the warp goes on with the next 32 columns while that store drains.
+                    const uint32_t out = smem_base + L::kOffOut + (uint32_t)(warp - 2) * L::kStageOutBytes;
+                    if (lane == 0) ptx::bulk_wait_group_read0();   // the previous block of this warp has been read out
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(out + (uint32_t)j * 64u + (uint32_t)lane * 2u),
+                                     "h"(__bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j]) * scale))) : "memory");
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tmap_c, out, (int)(n0 + q * 32u), (int)(m0 + col));
+                        ptx::bulk_commit_group();
+                    }
                 } else if (nn < p.n) {
                     const uint32_t mrow = m0 + col;
                     if (p.c_f32) {
@@ -566,6 +589,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
     }
 
     // ---- teardown: every thread gets here, also after an abort ----
+    if (p.c_tma && warp >= 2 && warp < 2 + kWorkerWarps && lane == 0) ptx::bulk_wait_group0();   // this warp's tile stores are complete
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (p.ts && threadIdx.x == 0) atomicMax(p.ts + 1, ptx::globaltimer());
@@ -630,6 +654,16 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
                     BITS == 8 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc) return rc;
     TsParams p;
+    // bf16 C of a plain GEMM leaves through tile stores (32 channels x 32 rows per store); every other form stores from registers
+    CUtensorMap tc = ta;
+    p.c_tma = 0;
+    {
+        const char* e = getenv("AFB_PREFILL_TILE_STORE");   // tuning aid: 0 switches it off
+        const bool wanted = !(e && atoi(e) == 0);
+        if (wanted && !(a.flags & AFB_FLAG_C_F32) && !tile_done && !push && !fused && a.ldc % 8 == 0 && (uintptr_t)a.ptr_c % 16 == 0 &&
+            ts_tmap_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.ptr_c, a.n, a.m, (uint64_t)a.ldc * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE) == AFB_OK)
+            p.c_tma = 1;
+    }
     p.c = reinterpret_cast<uint16_t*>(a.ptr_c);
     p.scale = a.ptr_scale;
     p.zero = reinterpret_cast<const uint8_t*>(a.ptr_zero);
@@ -696,7 +730,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
-    kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, p);
+    kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, tc, p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);
