@@ -248,6 +248,20 @@ def test_leading_dimensions_larger_than_the_matrix(afb, oracle, variant, m, flag
     check_close(oracle, oracle.gemm(case, threads=4), got, f"padded leading dimensions, int{bits}")
 
 
+@pytest.mark.parametrize("m,n,k,ldc", [(300, 264, 320, 264), (259, 136, 128, 160), (1024, 512, 512, 512)])
+def test_prefill_tile_stores_equal_register_stores(afb, oracle, monkeypatch, m, n, k, ldc):
+    """A plain bf16 result leaves the prefill kernel through shared memory and 32 x 32 tile stores (clipped at the edges of C);
+    AFB_PREFILL_TILE_STORE=0 stores the same values from registers.  Same bits, and the padding of C stays untouched."""
+    case = T.make_case(m, n, k, seed=77)
+    got_tile, raw_tile = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=pkg.FLAG_PREFILL_TMEM_A, ldc=ldc, guard=4096)
+    monkeypatch.setenv("AFB_PREFILL_TILE_STORE", "0")
+    got_reg, raw_reg = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=pkg.FLAG_PREFILL_TMEM_A, ldc=ldc, guard=4096)
+    assert np.array_equal(got_tile.view(np.uint16), got_reg.view(np.uint16))
+    assert np.array_equal(raw_tile, raw_reg)   # guard bytes and ldc padding included
+    check_close(oracle, oracle.gemm(case, threads=4), got_tile, "tile stores")
+    assert afb.read_status()[0] == 0
+
+
 def test_gemm_publishing_tiles_and_tile_exchange_on_one_rank(afb, oracle):
     """The tile-granular K-split exchange with a single rank: the GEMM counts its tiles, the exchange kernel waits for the
     counts, rounds the fp32 partial sums to bf16 and stores C.  (Several ranks: tests/test_dist.py on a multi-GPU box.)"""
