@@ -70,6 +70,9 @@ int launch_decode(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);
 int launch_decode_ws(const afb_gemm_args& a, DeviceCtx* ctx, float* ws, size_t ws_bytes, uint32_t* counters,
                      size_t counter_count, cudaStream_t s);
 int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);      // converted weights through shared memory
+// SMs the pushing GEMM of the pipelined reduce-scatter leaves free for the kernel that sums and broadcasts next to it
+// (environment variable AFB_SUB_AR_SMS, default 16: on 2 GPUs 1.03 ms for the down-projection with 16, 1.13 with 8)
+uint32_t sub_allreduce_sms();
 int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, const afb_fused_args* fused = nullptr);   // converted weights in tensor memory
 int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* tile_done, cudaStream_t s);
 int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s,

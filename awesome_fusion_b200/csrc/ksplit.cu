@@ -30,6 +30,14 @@ struct ARParams {
     unsigned long long* ts;   // optional phase timestamps (nullptr = off)
 };
 
+// Polling load without ordering: a kernel that polls NEXT TO a GEMM on the same SM must not issue an acquire per probe (every
+// system-scope acquire disturbs the caches the GEMM's CTA lives on: measured 1.85 x on the co-resident CTA, and with a static
+// tile assignment on the whole GEMM); it probes with this, sleeps between probes, and orders once after the value has shown.
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -180,12 +188,11 @@ __global__ void __launch_bounds__(128, 6) ksplit_sub_allreduce_kernel(const SubA
             const unsigned long long t0 = now_ns();
             bool ok = true;
             uint32_t spins = 0;
-            while ((int32_t)(ld_acquire_sys(sp.counters + c) - sp.want) < 0) {
-                if ((++spins & 0xfu) == 0) {
-                    if (now_ns() - t0 > p.wait_ns) { ok = false; break; }
-                    __nanosleep(200);
-                }
+            while ((int32_t)(ld_relaxed_sys(sp.counters + c) - sp.want) < 0) {
+                __nanosleep(500);
+                if ((++spins & 0xfu) == 0 && now_ns() - t0 > p.wait_ns) { ok = false; break; }
             }
+            if (ok) (void)ld_acquire_sys(sp.counters + c);   // the one ordered load: the counted tiles are visible from here on
             if (!ok && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 14; p.status[2] = (int)c; p.status[3] = (int)p.epoch; }
             s_ok = ok ? 1u : 0u;
             if (p.ts && blockIdx.x == 0 && c + 1 == sp.sub_blocks) p.ts[3] = now_ns();
@@ -507,20 +514,31 @@ extern "C" int afb_ksplit_sub_allreduce_launch(const afb_sub_allreduce_args* sa,
     p.status = ctx->status;
     p.ts = phase_ts_if_enabled(ctx);
     sp.counters = sa->counters; sp.sub_blocks = sa->sub_blocks; sp.want = per_chunk * sa->launches;
-    // next to the GEMM's CTA on an SM: same shared-memory carve-out as the GEMM, or the two never co-reside (see the tile-granular form)
+    // This kernel runs on SMs of its own: the pushing GEMM leaves sub_allreduce_sms() SMs free, and every CTA here asks for a
+    // sixth of an SM's shared memory (which it does not use), so that six of them (the register limit of the launch bounds)
+    // fill a free SM and none fits next to a CTA of the GEMM.  Next to one it cost the GEMM a factor 1.7 (measured on 2 GPUs, whatever it did there: polling, sleeping or
+    // summing), and with the GEMM's static tile assignment one slowed CTA is the whole GEMM.
+    constexpr int kCtasPerSm = 6, kSmemPerCta = 36 * 1024;
     static DeviceOnce carveout_set;
     if (!carveout_set.done(ctx->device)) {
         cudaError_t e = cudaFuncSetAttribute(ksplit_sub_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return cuda_fail(e);
         carveout_set.mark(ctx->device);
     }
-    // 128 threads with at most 80 registers each (launch bounds): 10 240 registers, which fit next to the GEMM's 320 x 168
-    static const int ctas = [] { const char* e = getenv("AFB_SUB_AR_CTAS"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 148) ? v : 64; }();
-    ksplit_sub_allreduce_kernel<<<ctas, 128, 0, (cudaStream_t)stream>>>(sp);
+    static const int ctas_env = [] { const char* e = getenv("AFB_SUB_AR_CTAS"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 1184) ? v : 0; }();
+    const int ctas = ctas_env ? ctas_env : (int)sub_allreduce_sms() * kCtasPerSm;
+    ksplit_sub_allreduce_kernel<<<ctas, 128, kSmemPerCta, (cudaStream_t)stream>>>(sp);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);
 }
+
+namespace afb {
+uint32_t sub_allreduce_sms() {
+    static const uint32_t n = [] { const char* e = getenv("AFB_SUB_AR_SMS"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 64) ? (uint32_t)v : 16u; }();
+    return n;
+}
+}  // namespace afb
 
 extern "C" int afb_ksplit_tile_allreduce_launch(const afb_tile_allreduce_args* ta, void* stream) {
     if (!ta) return AFB_ERR_BAD_ARG;

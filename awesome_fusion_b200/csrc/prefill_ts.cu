@@ -91,7 +91,7 @@ struct TsLayout {
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     // epilogue staging: one [32 activation rows][32 channels] bf16 block (2 KiB) per converter warp, the source of a tile store
     static constexpr int kStageOutBytes = 32 * 32 * 2;
-    static constexpr int kOffOut = (kOffMisc + 16 + 127) / 128 * 128;
+    static constexpr int kOffOut = (kOffMisc + 32 + 127) / 128 * 128;   // 8 words of flags and counters before it
     static constexpr int kDynamic = kOffOut + kWorkerWarps * kStageOutBytes + 1024;
     static constexpr uint32_t kTmemCols = 512;                   // accumulator [0, BMA) + weight slots [256, 256 + kSlotsA * 32)
     static constexpr uint32_t kColA = 256;
@@ -187,6 +187,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         ptx::mbar_init(bar_tail_stored, kWorkerWarps);
         ptx::mbar_init(bar_tail_verdict, 1);
         *abort_flag = 0;
+        tmem_slot[4] = 0; tmem_slot[5] = 0;   // converter warps that have reported the tile being counted (pipelined reduce-scatter), by tile parity
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmap_act);
         ptx::prefetch_tmap(&tmap_w);
@@ -295,6 +296,31 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         uint32_t st = 0, ph = 0, sa = 0, pa = 0, it = 0;
         bool ok = true;
         Item w;
+        // Pipelined reduce-scatter: a finished tile is counted at its owner only after this warp's peer stores of the tile are
+        // visible system-wide, and a fence right after the stores would wait for them to drain over NVLink (tens of microseconds
+        // at a CTA's share of the link) with the accumulator and the converters held up.  The count of a tile is therefore taken
+        // one tile later, at the start of the next epilogue, when those stores have long drained and the fence is cheap; the last
+        // tile of the CTA is counted after the loop.
+        // The eight converter warps of the CTA meet at a word in shared memory and the last one reports the whole tile with ONE
+        // remote addition of 8: the counters are few (one per owner and column chunk), and an addition per warp means thousands of
+        // system-scope atomics from every GPU on the same few words.
+        // (two words, used in turn: a warp can be at most one tile ahead of another, so the arrivals of consecutive tiles never mix)
+        uint32_t* pending_cnt = nullptr;
+        uint32_t pending_parity = 0;
+        auto count_pending = [&]() {
+            if (!pending_cnt) return;
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // this lane's peer stores of the tile, before the arrival below
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t* arrivals = const_cast<uint32_t*>(tmem_slot) + 4 + pending_parity;
+                if (atomicAdd(arrivals, 1u) == (uint32_t)kWorkerWarps - 1) {   // every warp of the CTA has fenced its stores
+                    atomicExch(arrivals, 0u);   // this word is used again two tiles from now
+                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(pending_cnt), "r"((uint32_t)kWorkerWarps) : "memory");
+                }
+            }
+            pending_cnt = nullptr;
+        };
         for (; ok && get_item(it, w); ++it) {
             const uint32_t t = w.t;
             uint32_t mt_, nt_;
@@ -394,6 +420,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 break;
             }
             ptx::tc_fence_after_sync();
+            count_pending();   // the previous tile of this CTA (pipelined reduce-scatter only)
             float scale = 1.f;
             if (!GROUPED && nn < p.n)
                 scale = p.scale_dtype == AFB_SCALE_BF16 ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(p.scale)[nn] << 16)
@@ -541,18 +568,18 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                     if (tid == 0) p.tail_counters[w.tail_r] = 0u;   // ready for the next launch
                 }
             }
-            if (p.push_sub) __threadfence_system();   // this lane's peer stores of the tile are visible system-wide before the count below
-            if (p.push_sub) __syncwarp();
             if (lane == 0) {
                 ptx::mbar_arrive(bar_acc_empty);
                 if (p.push_on == 2) ptx::mbar_arrive(bar_tile_stored);
                 if (p.tile_done) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.tile_done + t), "r"(1u) : "memory");
-                if (p.push_sub) {   // one count per converter warp and tile, at the owner of the tile's rows, for the tile's column chunk
-                    const uint32_t owner = m0 / p.push_rows, chunk = nt_ / (p.n_tiles / p.push_sub);
-                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_cnt[owner] + chunk), "r"(1u) : "memory");
-                }
+            }
+            if (p.push_sub) {   // one count per converter warp and tile, at the owner of the tile's rows, for the tile's column chunk
+                const uint32_t owner = m0 / p.push_rows, chunk = nt_ / (p.n_tiles / p.push_sub);
+                pending_cnt = p.push_cnt[owner] + chunk;
+                pending_parity = it & 1u;
             }
         }
+        count_pending();   // the last tile of this CTA: here the fence does wait for the tile's stores to drain
     }
 
     else if (p.push_on == 2) {
@@ -729,7 +756,9 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
         attr_set.mark(ctx->device);
     }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
-    const uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    // pipelined reduce-scatter: a few SMs are left to the kernel that sums and broadcasts the finished column chunks (ksplit.cu)
+    if (p.push_sub && grid == (uint32_t)ctx->sm_count && grid > 2 * sub_allreduce_sms()) grid -= sub_allreduce_sms();
     kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, tc, p);
     count_launch();
     cudaError_t e = cudaGetLastError();
