@@ -174,7 +174,7 @@ struct SubARParams {
     uint32_t sub_blocks, want;  // want = counts per chunk and launch x launches so far
 };
 
-__global__ void __launch_bounds__(128, 6) ksplit_sub_allreduce_kernel(const SubARParams sp) {
+__global__ void __launch_bounds__(768, 1) ksplit_sub_allreduce_kernel(const SubARParams sp) {
     const ARParams& p = sp.ar;
     __shared__ uint32_t s_ok;
     __shared__ uint32_t s_last;
@@ -514,20 +514,20 @@ extern "C" int afb_ksplit_sub_allreduce_launch(const afb_sub_allreduce_args* sa,
     p.status = ctx->status;
     p.ts = phase_ts_if_enabled(ctx);
     sp.counters = sa->counters; sp.sub_blocks = sa->sub_blocks; sp.want = per_chunk * sa->launches;
-    // This kernel runs on SMs of its own: the pushing GEMM leaves sub_allreduce_sms() SMs free, and every CTA here asks for a
-    // sixth of an SM's shared memory (which it does not use), so that six of them (the register limit of the launch bounds)
-    // fill a free SM and none fits next to a CTA of the GEMM.  Next to one it cost the GEMM a factor 1.7 (measured on 2 GPUs, whatever it did there: polling, sleeping or
+    // This kernel runs on SMs of its own: the pushing GEMM leaves sub_allreduce_sms() SMs free, and this kernel is as many CTAs
+    // of 768 threads, each asking for most of an SM's shared memory (which it does not use): one CTA per SM, none fits next to a
+    // CTA of the GEMM, and whichever kernel reaches the GPU first, the other still finds the SMs it needs (a CTA of this kernel
+    // that sat on an SM the GEMM needs would wait for tiles that cannot be computed).  Next to one it cost the GEMM a factor 1.7 (measured on 2 GPUs, whatever it did there: polling, sleeping or
     // summing), and with the GEMM's static tile assignment one slowed CTA is the whole GEMM.
-    constexpr int kCtasPerSm = 6, kSmemPerCta = 36 * 1024;
+    constexpr int kThreads = 768, kSmemPerCta = 200 * 1024;
     static DeviceOnce carveout_set;
     if (!carveout_set.done(ctx->device)) {
         cudaError_t e = cudaFuncSetAttribute(ksplit_sub_allreduce_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(ksplit_sub_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerCta);
         if (e != cudaSuccess) return cuda_fail(e);
         carveout_set.mark(ctx->device);
     }
-    static const int ctas_env = [] { const char* e = getenv("AFB_SUB_AR_CTAS"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 1184) ? v : 0; }();
-    const int ctas = ctas_env ? ctas_env : (int)sub_allreduce_sms() * kCtasPerSm;
-    ksplit_sub_allreduce_kernel<<<ctas, 128, kSmemPerCta, (cudaStream_t)stream>>>(sp);
+    ksplit_sub_allreduce_kernel<<<sub_allreduce_sms(), kThreads, kSmemPerCta, (cudaStream_t)stream>>>(sp);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);
