@@ -4,7 +4,7 @@
 // One persistent CTA per SM walks C tiles of 128 x BN.  Per 64-wide K step:
 //   warp 0      (1 lane)  TMA: A tile [128 x 64] bf16 (128-byte swizzle) and the RAW B tile
 //                         [BN x 64] int8 / int4 into a ring of stages            (reference: .s:247-286 global loads)
-//   warps 6-13  (256 thr) read the raw tile, unpack to exact bf16 in registers (dequant.cuh),
+//   warps 6-21  (512 thr) read the raw tile, unpack to exact bf16 in registers (dequant.cuh),
 //                         optionally multiply by the per-group scale, and write a K-major
 //                         128-byte-swizzled bf16 tile that tcgen05.mma can consume (reference: .dequant_int8_4x1, .s:18-55)
 //   warp 1      (1 lane)  tcgen05.mma kind::f16, 128 x BN x 16, fp32 accumulators in TMEM (reference: MFMA macro .s:57-94)
@@ -25,9 +25,9 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kStagesA = 4;   // A + raw-B ring
 constexpr int kStagesB = 3;   // converted-B ring
-constexpr int kConvWarps = 8;
+constexpr int kConvWarps = 16;   // measured against 8: 84 vs 90 us (int4 group-128, 28672 x 8192, M <= 128), 94 vs 105 us (int8): more chains in flight
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = 32 * (2 + kEpiWarps + kConvWarps);  // 448
+constexpr int kThreads = 32 * (2 + kEpiWarps + kConvWarps);  // 704
 constexpr int kFirstConvWarp = 2 + kEpiWarps;   // warps 2 .. 2+kEpiWarps-1 are the epilogue
 
 struct PrefillParams {
@@ -248,9 +248,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else {
         // ======================= converters =======================
-        const int cid = threadIdx.x - kFirstConvWarp * 32;   // 0..255
+        const int cid = threadIdx.x - kFirstConvWarp * 32;   // 0..511
         constexpr int kPiecesPerRow = L::kRawRowBytes / 16;   // 4 (int8) or 2 (int4)
-        constexpr int kItems = BN * kPiecesPerRow / (kConvWarps * 32);
+        constexpr int kItems = (BN * kPiecesPerRow + kConvWarps * 32 - 1) / (kConvWarps * 32);   // the last item may be empty for some threads
         const uint32_t xormask = (BITS == 8 && p.enc == AFB_ENC_OFFSET_BINARY) ? 0x80808080u : 0u;
         const uint32_t magic4 = p.enc == AFB_ENC_OFFSET_BINARY ? 0x43004300u : 0x43084308u;
         const uint32_t groups_per_row = GROUPED ? p.k / p.group : 0;
@@ -263,7 +263,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             auto load_scale = [&](int itx, uint32_t gidx) -> uint32_t {
                 const uint32_t rowi = (uint32_t)(itx * (kConvWarps * 32) + cid) / kPiecesPerRow;
                 const uint32_t nn = n0 + rowi;
-                if (nn >= p.n || gidx >= groups_per_row) return (uint32_t)0;
+                if (rowi >= (uint32_t)BN || nn >= p.n || gidx >= groups_per_row) return (uint32_t)0;
                 return bf16_dup(reinterpret_cast<const uint16_t*>(p.scale)[(size_t)nn * groups_per_row + gidx]);
             };
             if (GROUPED) {
@@ -285,6 +285,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                 for (int itx = 0; itx < kItems; ++itx) {
                     const uint32_t id = (uint32_t)(itx * (kConvWarps * 32) + cid);
+                    if (id >= (uint32_t)(BN * kPiecesPerRow)) continue;
                     const uint32_t rowi = id / kPiecesPerRow, piece = id % kPiecesPerRow;
                     const uint4 w4 = *reinterpret_cast<const uint4*>(raw + rowi * L::kRawRowBytes + piece * 16);
                     const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
