@@ -268,8 +268,10 @@ int afb_gemm_launch(const afb_gemm_args* args, void* stream) {
                     // tiles each needs (28672 channels: 112 vs 224 tiles on 148 SMs -> shared-memory form; 8192: 32 vs 64 -> the other)
                     const uint64_t sms = (uint64_t)ctx->sm_count, mt = (args->m + 127) / 128;
                     const uint64_t waves_ss = (mt * ((args->n + 255) / 256) + sms - 1) / sms;
-                    const uint64_t waves_ts = (mt * ((args->n + 127) / 128) + sms - 1) / sms;
-                    ts = waves_ts * 7 < waves_ss * 10;
+                    const uint64_t tiles_ts = mt * ((args->n + 127) / 128), waves_ts = (tiles_ts + sms - 1) / sms;
+                    // at most half a wave of tiles: the tensor-memory form cuts every tile into up to 4 stretches of K
+                    const uint64_t parts_ts = tiles_ts * 2 <= sms ? (sms / tiles_ts < 4 ? sms / tiles_ts : 4) : 1;
+                    ts = waves_ts * 7 < waves_ss * 10 * parts_ts;
                 }
             }
             if (args->flags & AFB_FLAG_PREFILL_SMEM_B) ts = false;

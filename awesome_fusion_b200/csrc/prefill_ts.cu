@@ -704,12 +704,13 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.group_m = tile_done ? p.m_tiles : pick_group_m(a, p.m_tiles, p.n_tiles, BMA, ctx->sm_count);   // the exchange kernel assumes row-tile-fastest order
     p.tile_done = tile_done;
     // The tiles beyond the last full wave would keep a few SMs busy for a whole tile while the rest idle: cut each of them into
-    // up to 4 stretches of K, one per CTA (up-projection shard on 8 GPUs: 448 tiles on 148 SMs = 3 waves + 4 tiles).
+    // up to 4 stretches of K, one per CTA (up-projection shard on 8 GPUs: 448 tiles on 148 SMs = 3 waves + 4 tiles).  The same
+    // when ALL the tiles are at most half a wave (8192 channels at M <= 128: 64 tiles, two stretches each on 128 SMs).
     p.tail_first = p.m_tiles * p.n_tiles; p.tail_tiles = 0; p.tail_parts = 0;
     p.tail_ws = nullptr; p.tail_counters = nullptr;
     {
         const uint32_t tiles_all = p.m_tiles * p.n_tiles, sms = (uint32_t)ctx->sm_count, nkb = a.k / BK;
-        const uint32_t rest = tiles_all > sms ? tiles_all % sms : 0;
+        const uint32_t rest = tiles_all > sms ? tiles_all % sms : (tiles_all < sms ? tiles_all : 0);
         const char* e = getenv("AFB_PREFILL_SPLIT_TAIL");   // tuning aid: 0 switches it off
         const bool allowed = !(e && atoi(e) == 0) && !tile_done && !push && !fused && a.n % 4 == 0;
         if (allowed && rest > 0 && rest <= sms / 2) {
@@ -759,6 +760,7 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
     // pipelined reduce-scatter: a few SMs are left to the kernel that sums and broadcasts the finished column chunks (ksplit.cu)
     if (p.push_sub && grid == (uint32_t)ctx->sm_count && grid > 2 * sub_allreduce_sms()) grid -= sub_allreduce_sms();
+    if (grid < p.tail_tiles * p.tail_parts) grid = p.tail_tiles * p.tail_parts;   // less than a wave of tiles, all of them cut along K
     kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, tc, p);
     count_launch();
     cudaError_t e = cudaGetLastError();
