@@ -759,7 +759,10 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
     // pipelined reduce-scatter: a few SMs are left to the kernel that sums and broadcasts the finished column chunks (ksplit.cu)
-    if (p.push_sub && grid == (uint32_t)ctx->sm_count && grid > 2 * sub_allreduce_sms()) grid -= sub_allreduce_sms();
+    // (always that many, also when there are fewer tiles than SMs: a CTA of that kernel on an SM this GEMM still needs would
+    // wait for tiles that cannot be computed)
+    if (p.push_sub && (uint32_t)ctx->sm_count > 2 * sub_allreduce_sms() && grid > (uint32_t)ctx->sm_count - sub_allreduce_sms())
+        grid = (uint32_t)ctx->sm_count - sub_allreduce_sms();
     if (grid < p.tail_tiles * p.tail_parts) grid = p.tail_tiles * p.tail_parts;   // less than a wave of tiles, all of them cut along K
     kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, tc, p);
     count_launch();
