@@ -291,8 +291,9 @@ int afb_dist_split_range(uint32_t total, uint32_t world, uint32_t rank, uint32_t
  * cut into `sub_blocks` chunks) and, inside a chunk, owner by owner starting with its own rank, so that every `world` units one
  * more chunk of EVERY rank's rows is complete in that rank's staging slots; each finished tile is counted in
  * counters[owner][chunk] (uint32[sub_blocks] per rank, zero before first use, only grow).  afb_ksplit_sub_allreduce_launch,
- * launched on ANOTHER stream so that it runs next to the GEMM, waits for a chunk's count, sums the LOCAL slots in rank order,
- * rounds and broadcasts it while the GEMM works on the next chunk: only the last chunk is left after the GEMM.  base.partial[q]
+ * launched on ANOTHER stream so that it runs next to the GEMM (on SMs of its own: the pipelined GEMM's grid leaves
+ * AFB_SUB_AR_SMS of them free, default 16, and the two kernels never share an SM), waits for a chunk's count, sums the LOCAL
+ * slots in rank order, rounds and broadcasts it while the GEMM works on the next chunk: only the last chunk is left after the GEMM.  base.partial[q]
  * are the local slots as for afb_gemm_launch_push; base.signals / epoch as for afb_ksplit_allreduce_launch; `launches` = how
  * many pipelined GEMMs have been issued on these counters (same on all ranks).  N must be a multiple of 128 * sub_blocks. */
 typedef struct afb_sub_allreduce_args {

@@ -428,6 +428,26 @@ def test_prefill_tail_tiles_split_along_k(afb, oracle, monkeypatch, bits, group,
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k,bits,group", [(96, 1024, 4096, 8, 0), (200, 2048, 2048, 8, 0), (128, 1024, 4096, 4, 128)])
+def test_prefill_less_than_half_a_wave_of_tiles_split_along_k(afb, oracle, monkeypatch, m, n, k, bits, group):
+    """At most half a wave of tiles (8 or 16 tiles on 148 SMs): every tile is cut into stretches of K for different CTAs, as the
+    tiles of a short last wave are.  Checked against the oracle, for repeatability, and against the same GEMM without the cut."""
+    case = T.make_case(m, n, k, bits=bits, group=group, seed=93)
+    ref = oracle.gemm(case, threads=8, round_w=True) if group else oracle.gemm(case, threads=8)
+    flags = pkg.FLAG_PREFILL_TMEM_A
+    a, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags)
+    b, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags)
+    assert np.array_equal(a, b), "two runs differ"
+    monkeypatch.setenv("AFB_PREFILL_SPLIT_TAIL", "0")
+    whole, _ = T.run_case(afb, case, variant=pkg.VARIANT_PREFILL, flags=flags)
+    assert afb.read_status()[0] == 0
+    check_close(oracle, ref, a, "every tile cut along K")
+    check_close(oracle, ref, whole, "tiles whole")
+    # the cut changes the order of the fp32 additions: most results still round to the same bf16
+    assert np.mean(a == whole) > 0.9
+
+
+@pytest.mark.gpu
 def test_measurement_aids_do_not_disturb_the_device(afb, oracle):
     """afb_probe_launch (empty and read-only kernels with a decode-like launch shape, with and without programmatic dependent
     launch) and afb_phase_timestamps answer with a status, and a GEMM right after them is still correct."""
