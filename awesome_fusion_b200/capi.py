@@ -34,7 +34,7 @@ EXPORTS = [
     "afb_gemm_host", "afb_gemm_host_async", "afb_gemm_host_wait", "afb_gemm_launch_static", "afb_prepack", "afb_prepack_gated", "afb_gemm_fused_launch", "afb_dequant_dump", "afb_read_status", "afb_ipc_export", "afb_ipc_import", "afb_ipc_release",
     "afb_ksplit_allreduce_launch", "afb_cast_f32_to_bf16", "afb_ksplit_tile_info", "afb_gemm_launch_tiles", "afb_ksplit_tile_allreduce_launch", "afb_gemm_launch_push", "afb_abi_sizes",
     "afb_dist_init", "afb_dist_world", "afb_dist_stream", "afb_dist_gemm_launch", "afb_dist_sync", "afb_dist_finalize", "afb_dist_split_range",
-    "afb_ksplit_sub_info", "afb_gemm_launch_push_pipelined", "afb_ksplit_sub_allreduce_launch", "afb_probe_launch", "afb_phase_timestamps", "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
+    "afb_ksplit_sub_info", "afb_gemm_launch_push_pipelined", "afb_ksplit_sub_allreduce_launch", "afb_gemm_launch_push_exchange", "afb_probe_launch", "afb_phase_timestamps", "afb_status_string", "afb_last_cuda_error", "afb_last_cuda_error_string", "afb_launch_count", "afb_version",
 ]
 
 

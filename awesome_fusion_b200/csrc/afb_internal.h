@@ -75,8 +75,20 @@ int launch_prefill(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s);     
 uint32_t sub_allreduce_sms();
 int launch_prefill_ts(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, const afb_fused_args* fused = nullptr);   // converted weights in tensor memory
 int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* tile_done, cudaStream_t s);
+// The sum and broadcast of the pipelined reduce-scatter done inside the pushing GEMM, by two extra warps of every CTA (so that no
+// second kernel has to share SMs with the GEMM): where the finished rows go, the words of the closing signal round, the count
+// every chunk counter of this rank has to reach.
+struct PushExchange {
+    uint16_t* c[AFB_MAX_RANKS];
+    uint16_t* c_multicast;
+    uint32_t* signals[AFB_MAX_RANKS];
+    const uint32_t* counters;     // this rank's per-chunk counters
+    uint32_t ldc, epoch, want;
+    unsigned long long wait_ns;
+    uint32_t* cta_done;           // device uint32[2]: warps finished, any failed (zero between launches)
+};
 int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s,
-                           uint32_t* const* counters = nullptr, uint32_t sub_blocks = 0);
+                           uint32_t* const* counters = nullptr, uint32_t sub_blocks = 0, const PushExchange* x = nullptr);
 void prefill_ts_tile_info(uint32_t m, uint32_t n, uint32_t* tile_m, uint32_t* tile_n, uint32_t* m_tiles, uint32_t* n_tiles, uint32_t* arrivals);
 int launch_probe(uint32_t kind, const void* src, size_t bytes, uint32_t ctas, uint32_t smem_bytes, bool pdl, uint32_t* sink, cudaStream_t s);
 int launch_dequant_dump(const afb_gemm_args& a, void* out, cudaStream_t s);

@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <cuda_bf16.h>
 #include "afb_internal.h"
+#include "sys_sync.cuh"
 
 namespace afb {
 namespace {
@@ -30,52 +31,7 @@ struct ARParams {
     unsigned long long* ts;   // optional phase timestamps (nullptr = off)
 };
 
-// Polling load without ordering: a kernel that polls NEXT TO a GEMM on the same SM must not issue an acquire per probe (every
-// system-scope acquire disturbs the caches the GEMM's CTA lives on: measured 1.85 x on the co-resident CTA, and with a static
-// tile assignment on the whole GEMM); it probes with this, sleeps between probes, and orders once after the value has shown.
-__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Waits until signals[phase][q] >= epoch for every rank q.  One thread calls it.  false = gave up.
-__device__ bool wait_all(const uint32_t* my_signals, int phase, uint32_t world, uint32_t epoch, unsigned long long limit_ns) {
-    const unsigned long long t0 = now_ns();
-    for (uint32_t q = 0; q < world; ++q) {
-        const uint32_t* f = my_signals + phase * AFB_MAX_RANKS + q;
-        uint32_t spins = 0;
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-            if ((++spins & 0x3fu) == 0 && now_ns() - t0 > limit_ns) return false;
-        }
-    }
-    return true;
-}
-
-// One 16-byte store to a multicast address: the switch writes it into every rank's copy of the buffer.
-__device__ __forceinline__ void st16_multicast(void* p, const uint4& v) {
-    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
-                 "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
-}
-__device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
+using namespace xchg;
 
 template <bool F32>
 __global__ void __launch_bounds__(kThreads) ksplit_allreduce_kernel(const ARParams p) {
@@ -473,6 +429,39 @@ extern "C" int afb_gemm_launch_push_pipelined(const afb_gemm_args* args, void* c
     a.ptr_c = stage[rank];   // never written in this mode; keeps the common validation happy
     a.ldc = a.n;
     return launch_prefill_ts_push(a, ctx, stage, world, rank, (cudaStream_t)stream, counters, sub_blocks);
+}
+
+// The pipelined reduce-scatter in ONE launch: the pushing GEMM of afb_gemm_launch_push_pipelined plus two extra warps per CTA that
+// do what afb_ksplit_sub_allreduce_launch does (x describes it exactly as for that entry point).
+extern "C" int afb_gemm_launch_push_exchange(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t* const counters[AFB_MAX_RANKS],
+                                             uint32_t world, uint32_t rank, uint32_t sub_blocks, const afb_sub_allreduce_args* sa, void* stream) {
+    if (!args || !stage || !counters || !sa || !args->ptr_a || !args->ptr_b || !args->ptr_scale) return AFB_ERR_BAD_ARG;
+    if (args->m == 0 || args->n == 0 || args->k == 0 || args->reserved != 0) return AFB_ERR_BAD_ARG;
+    if (args->lda < args->k || args->ldb < args->k || args->b_layout == AFB_LAYOUT_ROW || args->b_layout > 2) return AFB_ERR_BAD_ARG;
+    if (!(args->flags & AFB_FLAG_C_F32)) return AFB_ERR_UNSUPPORTED;   // the partial sums travel as fp32
+    if (world == 0 || world > AFB_MAX_RANKS || rank >= world || sub_blocks == 0) return AFB_ERR_BAD_ARG;
+    for (uint32_t q = 0; q < world; ++q) if (!stage[q] || (uintptr_t)stage[q] % 16 || !counters[q]) return AFB_ERR_BAD_ARG;
+    const afb_allreduce_args* x = &sa->base;
+    if (x->world != world || x->rank != rank || x->m != args->m || x->n != args->n || x->ldc % 8 || x->ldc < x->n) return AFB_ERR_BAD_ARG;
+    if (x->epoch == 0 || x->reserved != 0 || !x->partial_f32 || sa->counters != counters[rank] || sa->sub_blocks != sub_blocks || sa->launches == 0 || sa->reserved != 0)
+        return AFB_ERR_BAD_ARG;
+    uint32_t per_chunk = 0;
+    if (afb_ksplit_sub_info(x->m, x->n, world, sub_blocks, &per_chunk) != AFB_OK) return AFB_ERR_UNSUPPORTED;
+    for (uint32_t q = 0; q < world; ++q) if (!x->c[q] || (uintptr_t)x->c[q] % 16 || !x->signals[q]) return AFB_ERR_BAD_ARG;
+    if ((uintptr_t)x->c_multicast % 16) return AFB_ERR_BAD_ARG;
+    DeviceCtx* ctx = current_ctx();
+    if (!ctx) return AFB_ERR_NOT_INIT;
+    PushExchange px = {};
+    for (uint32_t q = 0; q < world; ++q) { px.c[q] = reinterpret_cast<uint16_t*>(x->c[q]); px.signals[q] = x->signals[q]; }
+    px.c_multicast = reinterpret_cast<uint16_t*>(x->c_multicast);
+    px.counters = sa->counters;
+    px.ldc = x->ldc; px.epoch = x->epoch; px.want = per_chunk * sa->launches;
+    px.wait_ns = (unsigned long long)(x->wait_ms ? x->wait_ms : 2000u) * 1000000ull;
+    px.cta_done = ctx->ar_words + 2;   // the pair of the exchange kernels that run next to a GEMM: one form at a time
+    afb_gemm_args a = *args;
+    a.ptr_c = stage[rank];   // never written in this mode; keeps the common validation happy
+    a.ldc = a.n;
+    return launch_prefill_ts_push(a, ctx, stage, world, rank, (cudaStream_t)stream, counters, sub_blocks, &px);
 }
 
 extern "C" int afb_ksplit_sub_info(uint32_t m, uint32_t n, uint32_t world, uint32_t sub_blocks, uint32_t* counts_per_chunk) {

@@ -21,6 +21,7 @@
 #include "afb_internal.h"
 #include "dequant.cuh"
 #include "ptx_sm100.cuh"
+#include "sys_sync.cuh"
 
 namespace afb {
 
@@ -72,6 +73,8 @@ struct TsParams {
     // more column chunk is complete on EVERY owner.  Each finished tile is counted in push_cnt[owner][chunk] (system-scope release).
     uint32_t push_sub, push_world;
     uint32_t* push_cnt[AFB_MAX_RANKS];
+    uint32_t xchg_on;      // pipelined reduce-scatter finished in this kernel: two extra warps per CTA sum and broadcast the chunks
+    PushExchange x;
     uint32_t push_on;      // 0: off; 1: the epilogue stores to the owner directly; 2: the epilogue stores to p.c (local) and the
                            // forwarder warps copy each finished tile to its owner while the next tile is being computed
     int32_t* status;
@@ -582,6 +585,81 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         count_pending();   // the last tile of this CTA: here the fence does wait for the tile's stores to drain
     }
 
+    else if (p.xchg_on) {
+        // ======================= exchange warps (only launched with the in-kernel exchange) =======================
+        // The other half of the pipelined reduce-scatter, done here instead of by a second kernel (which would have to share SMs
+        // with this one): when a column chunk of THIS rank's rows is complete in its local slots (every rank's tiles of the chunk
+        // counted), all the exchange warps of the grid add the slots in rank order, round once and broadcast the chunk, while the
+        // rest of their CTAs compute the next chunks.  Reads are local; the result leaves as one multicast store (or one store per
+        // rank).  The last warp of the grid to finish tells every rank that this rank's rows are in place and waits for theirs.
+        const uint32_t fw = (uint32_t)(warp - (2 + kWorkerWarps));
+        const uint32_t gw = blockIdx.x * kFwdWarps + fw, nw = gridDim.x * kFwdWarps;
+        const uint32_t chunk_cols = p.n / p.push_sub, vec_per_row = chunk_cols / 8;
+        const uint32_t total = p.push_rows * vec_per_row;
+        const uint32_t row0 = p.push_rank * p.push_rows;
+        const float* slots = p.push[p.push_rank];
+        bool failed = false;
+        for (uint32_t c = 0; c < p.push_sub && !failed; ++c) {
+            uint32_t ok = 1u;
+            if (lane == 0) {
+                const unsigned long long t0 = ptx::globaltimer();
+                uint32_t spins = 0;
+                while ((int32_t)(xchg::ld_relaxed_sys(p.x.counters + c) - p.x.want) < 0) {
+                    __nanosleep(500);
+                    if ((++spins & 0xfu) == 0 && (*abort_flag || ptx::globaltimer() - t0 > p.x.wait_ns)) { ok = 0u; break; }
+                }
+                if (ok) (void)xchg::ld_acquire_sys(p.x.counters + c);   // the counted tiles are visible from here on
+                else if (atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 16; p.status[2] = (int)c; p.status[3] = (int)p.x.epoch; }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { failed = true; break; }
+            for (uint32_t i = gw * 32u + (uint32_t)lane; i < total; i += nw * 32u) {
+                const uint32_t lr = i / vec_per_row, col = c * chunk_cols + (i - lr * vec_per_row) * 8u;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int q0 = 0; q0 < AFB_MAX_RANKS; q0 += 4) {
+                    uint4 lo[4], hi[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (q0 + q < (int)p.push_world) {
+                            const float* src = slots + ((size_t)(q0 + q) * p.push_rows + lr) * p.ldc + col;
+                            lo[q] = __ldcg(reinterpret_cast<const uint4*>(src)); hi[q] = __ldcg(reinterpret_cast<const uint4*>(src + 4));
+                        }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)   // fixed rank order: identical bits wherever it is computed
+                        if (q0 + q < (int)p.push_world) {
+                            acc[0] += __uint_as_float(lo[q].x); acc[1] += __uint_as_float(lo[q].y); acc[2] += __uint_as_float(lo[q].z); acc[3] += __uint_as_float(lo[q].w);
+                            acc[4] += __uint_as_float(hi[q].x); acc[5] += __uint_as_float(hi[q].y); acc[6] += __uint_as_float(hi[q].z); acc[7] += __uint_as_float(hi[q].w);
+                        }
+                }
+                const uint4 out = make_uint4(xchg::pack_bf16(acc[0], acc[1]), xchg::pack_bf16(acc[2], acc[3]), xchg::pack_bf16(acc[4], acc[5]), xchg::pack_bf16(acc[6], acc[7]));
+                const size_t at = (size_t)(row0 + lr) * p.x.ldc + col;
+                if (p.x.c_multicast) {
+                    xchg::st16_multicast(p.x.c_multicast + at, out);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < AFB_MAX_RANKS; ++q)
+                        if (q < (int)p.push_world) *reinterpret_cast<uint4*>(p.x.c[q] + at) = out;
+                }
+            }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+            if (failed) atomicExch(p.x.cta_done + 1, 1u);
+            if (atomicAdd(p.x.cta_done, 1u) == nw - 1) {   // the last exchange warp of the grid
+                const bool any_failed = atomicExch(p.x.cta_done + 1, 0u) != 0;
+                *p.x.cta_done = 0u;
+                __threadfence_system();
+                if (!any_failed) {
+                    for (uint32_t q = 0; q < p.push_world; ++q) xchg::st_release_sys(p.x.signals[q] + 1 * AFB_MAX_RANKS + p.push_rank, p.x.epoch);
+                    const bool done = xchg::wait_all(p.x.signals[p.push_rank], 1, p.push_world, p.x.epoch, p.x.wait_ns);
+                    if (!done && atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 17; p.status[2] = (int)p.push_rank; p.status[3] = (int)p.x.epoch; }
+                }
+            }
+        }
+    }
+
     else if (p.push_on == 2) {
         // ======================= forwarders (only launched in forward mode) =======================
         // Copy each finished 256 x 128 fp32 tile from local memory to the staging buffer of the rank owning its rows: 512
@@ -670,7 +748,7 @@ uint32_t pick_group_m(const afb_gemm_args& a, uint32_t m_tiles, uint32_t n_tiles
 template <int BITS, bool GROUPED, int BMA>
 int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32_t* tile_done = nullptr, void* const* push = nullptr,
                   uint32_t push_world = 0, uint32_t push_rank = 0, bool push_via_local = false, const afb_fused_args* fused = nullptr,
-                  uint32_t* const* push_cnt = nullptr, uint32_t push_sub = 0) {
+                  uint32_t* const* push_cnt = nullptr, uint32_t push_sub = 0, const PushExchange* xchg_desc = nullptr) {
     using L = TsLayout<BITS, BMA>;
     static_assert(L::kDynamic <= 232448, "shared memory budget");
     CUtensorMap ta, tw;
@@ -710,7 +788,9 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.tail_ws = nullptr; p.tail_counters = nullptr;
     {
         const uint32_t tiles_all = p.m_tiles * p.n_tiles, sms = (uint32_t)ctx->sm_count, nkb = a.k / BK;
-        const uint32_t rest = tiles_all > sms ? tiles_all % sms : (tiles_all < sms ? tiles_all : 0);
+        // (less than a wave: only for bf16 results -- fp32 results are the partial sums of a row-parallel GEMM, which the exchange forms
+        // sum to identical bits only while every form adds along K in the same order)
+        const uint32_t rest = tiles_all > sms ? tiles_all % sms : ((tiles_all < sms && !(a.flags & AFB_FLAG_C_F32)) ? tiles_all : 0);
         const char* e = getenv("AFB_PREFILL_SPLIT_TAIL");   // tuning aid: 0 switches it off
         const bool allowed = !(e && atoi(e) == 0) && !tile_done && !push && !fused && a.n % 4 == 0;
         if (allowed && rest > 0 && rest <= sms / 2) {
@@ -745,6 +825,8 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     p.push_sub = (push && push_cnt) ? push_sub : 0;
     for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push_cnt[q] = (p.push_sub && q < push_world) ? push_cnt[q] : nullptr;
     if (p.push_sub) p.m_rot = 0;   // the unit order already spreads the owners
+    p.xchg_on = (p.push_sub && xchg_desc) ? 1u : 0u;
+    p.x = xchg_desc ? *xchg_desc : PushExchange{};
     p.push_rows = push ? a.m / push_world : 0;
     for (uint32_t q = 0; q < AFB_MAX_RANKS; ++q) p.push[q] = (push && q < push_world) ? reinterpret_cast<float*>(push[q]) : nullptr;
     p.status = ctx->status;
@@ -761,10 +843,10 @@ int launch_ts_cfg(const afb_gemm_args& a, DeviceCtx* ctx, cudaStream_t s, uint32
     // pipelined reduce-scatter: a few SMs are left to the kernel that sums and broadcasts the finished column chunks (ksplit.cu)
     // (always that many, also when there are fewer tiles than SMs: a CTA of that kernel on an SM this GEMM still needs would
     // wait for tiles that cannot be computed)
-    if (p.push_sub && (uint32_t)ctx->sm_count > 2 * sub_allreduce_sms() && grid > (uint32_t)ctx->sm_count - sub_allreduce_sms())
+    if (p.push_sub && !p.xchg_on && (uint32_t)ctx->sm_count > 2 * sub_allreduce_sms() && grid > (uint32_t)ctx->sm_count - sub_allreduce_sms())
         grid = (uint32_t)ctx->sm_count - sub_allreduce_sms();
     if (grid < p.tail_tiles * p.tail_parts) grid = p.tail_tiles * p.tail_parts;   // less than a wave of tiles, all of them cut along K
-    kern<<<grid, p.push_on == 2 ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, tc, p);
+    kern<<<grid, (p.push_on == 2 || p.xchg_on) ? kThreadsFwd : kThreads, L::kDynamic, s>>>(ta, tw, tc, p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AFB_OK : cuda_fail(e);
@@ -786,14 +868,15 @@ int launch_prefill_ts_tiles(const afb_gemm_args& a, DeviceCtx* ctx, uint32_t* ti
 // Row-parallel GEMM whose epilogue is the reduce-scatter: every tile of fp32 partial sums is stored straight into the staging
 // buffer of the rank that owns those rows (peer stores over NVLink), slot = this rank.
 int launch_prefill_ts_push(const afb_gemm_args& a, DeviceCtx* ctx, void* const* stage, uint32_t world, uint32_t rank, cudaStream_t s,
-                           uint32_t* const* counters, uint32_t sub_blocks) {
+                           uint32_t* const* counters, uint32_t sub_blocks, const PushExchange* x) {
     if (!prefill_supports(a) || a.group_size != 0 || a.b_bits != 8 || a.m <= 128) return AFB_ERR_UNSUPPORTED;
     if (world == 0 || world > AFB_MAX_RANKS || rank >= world || a.m % (world * 256) != 0 || a.ldc != a.n) return AFB_ERR_UNSUPPORTED;
     if (counters) {   // pipelined form: whole column chunks of channel tiles, epilogue stores straight to the owner
         const uint32_t n_tiles = (a.n + BNW - 1) / BNW;
         if (sub_blocks == 0 || n_tiles % sub_blocks != 0 || a.n % BNW != 0 || (a.flags & AFB_FLAG_PUSH_VIA_LOCAL)) return AFB_ERR_UNSUPPORTED;
     }
-    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank, (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) != 0, nullptr, counters, sub_blocks);
+    if (x && !counters) return AFB_ERR_BAD_ARG;
+    return launch_ts_cfg<8, false, 256>(a, ctx, s, nullptr, stage, world, rank, (a.flags & AFB_FLAG_PUSH_VIA_LOCAL) != 0, nullptr, counters, sub_blocks, x);
 }
 
 // `fused`: optional epilogue description (bias, activation, gate * up, residual); a.ptr_c / a.ldc describe the [M, N_out] result.

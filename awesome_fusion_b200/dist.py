@@ -232,6 +232,25 @@ class PeerExchange:
         f.argtypes = [ctypes.POINTER(SubAllReduceArgs), ctypes.c_void_p]
         self.lib.check(f(ctypes.byref(sa), stream), "afb_ksplit_sub_allreduce_launch")
 
+    def gemm_pushing_exchange(self, args, sub_blocks, stream=None):
+        """Both halves of the pipelined form in one launch: the pushing GEMM in column-chunk order, with two extra warps per CTA that
+        sum each finished chunk of this rank's rows from the local slots and broadcast it.  C is complete when the launch is."""
+        from .capi import GemmArgs
+        self.epoch += 1
+        self.sub_launches = getattr(self, "sub_launches", 0) + 1
+        sa = SubAllReduceArgs()
+        sa.base = self.args()
+        sa.base.epoch = self.epoch
+        for q in range(self.world):
+            sa.base.partial[q] = self.partial + push_slot_offset(q, self.rank, self.world, self.m, self.n)
+        sa.counters, sa.sub_blocks, sa.launches, sa.reserved = self.tile_done, sub_blocks, self.sub_launches, 0
+        f = self.lib.lib.afb_gemm_launch_push_exchange
+        f.argtypes = [ctypes.POINTER(GemmArgs), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint32, ctypes.c_uint32,
+                      ctypes.c_uint32, ctypes.POINTER(SubAllReduceArgs), ctypes.c_void_p]
+        stage = (ctypes.c_void_p * MAX_RANKS)(*[self.partials[q] for q in range(self.world)])
+        cnt = (ctypes.c_void_p * MAX_RANKS)(*[self.tds[q] for q in range(self.world)])
+        self.lib.check(f(ctypes.byref(args), stage, cnt, self.world, self.rank, sub_blocks, ctypes.byref(sa), stream), "afb_gemm_launch_push_exchange")
+
     def gemm_publishing_tiles(self, args, stream=None):
         """The K-split GEMM into this rank's partial-sum buffer, counting finished tiles for allreduce_tiles()."""
         f = self.lib.lib.afb_gemm_launch_tiles
@@ -317,6 +336,7 @@ class ShardedMLP:
         self.overlap = mode == "overlap"
         self.push = mode == "push"
         self.pipelined = mode == "pipelined"
+        self.inkernel = mode == "inkernel"
         # column chunks of the pipelined form: 8 (measured on 2 GPUs: 1.03 ms for the down-projection against 1.14 with 2 chunks,
         # whose last chunk leaves half of the sum and broadcast for after the GEMM); AFB_SUB_BLOCKS overrides
         self.sub_blocks = int(os.environ.get("AFB_SUB_BLOCKS", "8"))
@@ -325,6 +345,10 @@ class ShardedMLP:
                 raise pkg.AfbError(-4, "the pipelined exchange needs fp32 partial sums, M a multiple of 256 * world and N of 128 * sub-blocks", "")
             mode = "fused"
             self.side = torch.cuda.Stream()
+        if mode == "inkernel":
+            if partial != "f32" or m % (256 * world) != 0 or down_n % (128 * self.sub_blocks) != 0:
+                raise pkg.AfbError(-4, "the in-kernel exchange needs fp32 partial sums, M a multiple of 256 * world and N of 128 * sub-blocks", "")
+            mode = "fused"
         if mode == "overlap":
             mode = "fused"
             self.side = torch.cuda.Stream()
@@ -340,13 +364,15 @@ class ShardedMLP:
                 self.overlap = False
                 self.push = False
                 self.pipelined = False
-                if exchange in ("fused", "overlap", "push", "pipelined"):
+                self.inkernel = False
+                if exchange in ("fused", "overlap", "push", "pipelined", "inkernel"):
                     raise pkg.AfbError(-3, "peer-memory exchange unavailable", why)
                 if rank == 0:
                     print(f"peer memory unavailable ({why}); using the NCCL exchange", flush=True)
                 mode = "nccl"
         if mode == "fused":
-            self.exchange_name = (f"reduce-scatter in the GEMM epilogue in {self.sub_blocks} column chunks (peer stores of fp32 tiles), each chunk summed from local slots and broadcast next to the GEMM" if self.pipelined
+            self.exchange_name = (f"reduce-scatter in the GEMM epilogue in {self.sub_blocks} column chunks (peer stores of fp32 tiles), each chunk summed from local slots and broadcast by two extra warps of every GEMM CTA (one launch)" if self.inkernel
+                                  else f"reduce-scatter in the GEMM epilogue in {self.sub_blocks} column chunks (peer stores of fp32 tiles), each chunk summed from local slots and broadcast next to the GEMM" if self.pipelined
                                   else f"tile-granular peer-memory all-reduce overlapped with the GEMM ({partial} partial sums)" if self.overlap
                                   else "reduce-scatter in the GEMM epilogue (peer stores of fp32 tiles) + local sum and bf16 broadcast" if self.push
                                   else f"fused peer-memory all-reduce after the GEMM ({partial} partial sums)")
@@ -396,6 +422,11 @@ class ShardedMLP:
                 self.px.allreduce_tiles(self.side.cuda_stream)
                 done = self.side.record_event()
             torch.cuda.current_stream().wait_event(done)   # the step ends when C is complete on this rank
+            if events:
+                events[2].record()
+            return
+        if self.world > 1 and self.px is not None and self.inkernel:
+            self.px.gemm_pushing_exchange(self.args_down, self.sub_blocks, stream)
             if events:
                 events[2].record()
             return

@@ -530,7 +530,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="sharded-mlp", choices=["sharded-mlp", "decode-floor"] + sorted(SINGLE_CASES))
-    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "pipelined", "overlap", "fused", "nccl"])
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "pipelined", "inkernel", "overlap", "fused", "nccl"])
     ap.add_argument("--no-cases", action="store_true", help="skip the single-GPU case sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     args = ap.parse_args()

@@ -307,6 +307,12 @@ int afb_ksplit_sub_info(uint32_t m, uint32_t n, uint32_t world, uint32_t sub_blo
 int afb_gemm_launch_push_pipelined(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t* const counters[AFB_MAX_RANKS],
                                    uint32_t world, uint32_t rank, uint32_t sub_blocks, void* stream);
 int afb_ksplit_sub_allreduce_launch(const afb_sub_allreduce_args* args, void* stream);
+/* Both halves in ONE launch: the pushing GEMM of afb_gemm_launch_push_pipelined with two extra warps per CTA that do what
+ * afb_ksplit_sub_allreduce_launch does (x: exactly as for that entry point, with x->counters == counters[rank]), so that no second
+ * kernel shares the SMs with the GEMM.  When the launch has completed, this rank's C holds the complete result.  No counterpart in
+ * the reference (single GPU). */
+int afb_gemm_launch_push_exchange(const afb_gemm_args* args, void* const stage[AFB_MAX_RANKS], uint32_t* const counters[AFB_MAX_RANKS],
+                                  uint32_t world, uint32_t rank, uint32_t sub_blocks, const afb_sub_allreduce_args* x, void* stream);
 /* sizeof(afb_gemm_args), sizeof(afb_allreduce_args), sizeof(afb_tile_allreduce_args), sizeof(afb_fused_args) as this library was
  * compiled: a binding in another language compares them with its own declarations before the first call.  Needs no GPU. */
 int afb_abi_sizes(uint32_t sizes[4]);

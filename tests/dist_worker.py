@@ -210,6 +210,19 @@ def main():
         assert all(np.array_equal(outs[0], o) for o in outs_p), "pipelined exchange differs from GEMM + fused exchange"
         if rank == 0:
             print(f"pipelined (multicast address: {'yes' if px.c_multicast else 'no'}): bit-identical to the fused exchange", flush=True)
+        # the same in ONE launch: the sum and broadcast done by two extra warps of every GEMM CTA
+        outs_x = []
+        for step in range(3):
+            lib.memset(px.c, 0, mp * n * 2)
+            tdist.barrier(); torch.cuda.synchronize()
+            px.gemm_pushing_exchange(args, 4, stream)
+            torch.cuda.synchronize()
+            outs_x.append(lib.to_host(px.c, (mp, n), np.uint16))
+        st = lib.read_status()
+        assert st[0] == 0, f"device status {st}"
+        assert all(np.array_equal(outs[0], o) for o in outs_x), "in-kernel exchange differs from GEMM + fused exchange"
+        if rank == 0:
+            print(f"in-kernel exchange (multicast address: {'yes' if px.c_multicast else 'no'}): bit-identical to the fused exchange", flush=True)
         px.close()
         for p in (p_a, p_b, p_s):
             lib.free(p)
