@@ -310,15 +310,18 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
         // (two words, used in turn: a warp can be at most one tile ahead of another, so the arrivals of consecutive tiles never mix)
         uint32_t* pending_cnt = nullptr;
         uint32_t pending_parity = 0;
+        // Ordering: a warp's lanes meet (__syncwarp), its lane 0 fences at CTA scope and arrives at the word; the last arrival fences
+        // at CTA scope again and performs the ONE system-scope release of the tile (cumulative over everything synchronised into
+        // it).  A system-scope fence per thread instead cost the GEMM 30 % on 4 GPUs (0.50 against 0.385 ms, whatever the chunk count).
         auto count_pending = [&]() {
             if (!pending_cnt) return;
-            asm volatile("fence.acq_rel.sys;" ::: "memory");   // this lane's peer stores of the tile, before the arrival below
             __syncwarp();
             if (lane == 0) {
                 uint32_t* arrivals = const_cast<uint32_t*>(tmem_slot) + 4 + pending_parity;
-                if (atomicAdd(arrivals, 1u) == (uint32_t)kWorkerWarps - 1) {   // every warp of the CTA has fenced its stores
+                __threadfence_block();
+                if (atomicAdd(arrivals, 1u) == (uint32_t)kWorkerWarps - 1) {   // every warp of the CTA has stored its part of the tile
                     atomicExch(arrivals, 0u);   // this word is used again two tiles from now
-                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                    __threadfence_block();
                     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(pending_cnt), "r"((uint32_t)kWorkerWarps) : "memory");
                 }
             }

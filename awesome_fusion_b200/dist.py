@@ -329,17 +329,20 @@ class ShardedMLP:
         import torch.distributed as tdist
         self.tdist = tdist
         mode = exchange
+        # column chunks of the pipelined forms: 8 (measured on 2 GPUs: 1.03 ms for the down-projection against 1.14 with 2 chunks,
+        # whose last chunk leaves half of the sum and broadcast for after the GEMM); AFB_SUB_BLOCKS overrides
+        self.sub_blocks = int(os.environ.get("AFB_SUB_BLOCKS", "8"))
         if mode == "auto":
             # measured: the reduce-scatter in the GEMM epilogue beats the exchange kernel after the GEMM, which beats the
-            # tile-granular exchange next to the GEMM (whose own NVLink traffic slows the GEMM by as much as the overlap saves)
-            mode = "push" if (partial == "f32" and m % (256 * world) == 0) else "fused"
+            # tile-granular exchange next to the GEMM (whose own NVLink traffic slows the GEMM by as much as the overlap saves);
+            # with the sum and broadcast done chunk by chunk by two extra warps of every GEMM CTA the tail after the GEMM goes too:
+            # 0.897 against 0.924 ms per step on 4 GPUs, 0.9225 against 0.930 ms for the down-projection on 2 (kept on push there)
+            pushable = partial == "f32" and m % (256 * world) == 0
+            mode = ("inkernel" if (pushable and world >= 4 and down_n % (128 * self.sub_blocks) == 0) else "push") if pushable else "fused"
         self.overlap = mode == "overlap"
         self.push = mode == "push"
         self.pipelined = mode == "pipelined"
         self.inkernel = mode == "inkernel"
-        # column chunks of the pipelined form: 8 (measured on 2 GPUs: 1.03 ms for the down-projection against 1.14 with 2 chunks,
-        # whose last chunk leaves half of the sum and broadcast for after the GEMM); AFB_SUB_BLOCKS overrides
-        self.sub_blocks = int(os.environ.get("AFB_SUB_BLOCKS", "8"))
         if mode == "pipelined":
             if partial != "f32" or m % (256 * world) != 0 or down_n % (128 * self.sub_blocks) != 0:
                 raise pkg.AfbError(-4, "the pipelined exchange needs fp32 partial sums, M a multiple of 256 * world and N of 128 * sub-blocks", "")
