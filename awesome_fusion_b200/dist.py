@@ -289,6 +289,20 @@ def cast_f32_to_bf16(lib, dst, src, rows, cols, stream=None):
     lib.check(f(dst, src, rows, cols, cols, cols, stream), "afb_cast_f32_to_bf16")
 
 
+def pick_exchange(world, partial, m, down_n, sub_blocks=8):
+    """The exchange form `auto` stands for.  Measured: the reduce-scatter in the GEMM epilogue ("push") beats the exchange kernel after
+    the GEMM ("fused"), which beats the tile-granular exchange next to the GEMM (whose own NVLink traffic slows the GEMM by as much as
+    the overlap saves); with the sum and broadcast done chunk by chunk by two extra warps of every GEMM CTA ("inkernel") the tail
+    after the GEMM goes too: 0.584 against 0.607 ms per step on 8 GPUs, 0.897 against 0.924 on 4, 0.9225 against 0.930 ms for the
+    down-projection on 2 (kept on push there).  Both need fp32 partial sums and M a multiple of 256 * world; the in-kernel form also
+    N a multiple of 128 * sub_blocks."""
+    if partial != "f32" or m % (256 * world) != 0:
+        return "fused"
+    if world >= 4 and down_n % (128 * sub_blocks) == 0:
+        return "inkernel"
+    return "push"
+
+
 class ShardedMLP:
     """The sharded benchmark step: column-parallel up-projection + row-parallel down-projection (int8, per-channel).
 
@@ -333,13 +347,7 @@ class ShardedMLP:
         # whose last chunk leaves half of the sum and broadcast for after the GEMM); AFB_SUB_BLOCKS overrides
         self.sub_blocks = int(os.environ.get("AFB_SUB_BLOCKS", "8"))
         if mode == "auto":
-            # measured: the reduce-scatter in the GEMM epilogue beats the exchange kernel after the GEMM, which beats the
-            # tile-granular exchange next to the GEMM (whose own NVLink traffic slows the GEMM by as much as the overlap saves);
-            # with the sum and broadcast done chunk by chunk by two extra warps of every GEMM CTA the tail after the GEMM goes too:
-            # 0.584 against 0.607 ms per step on 8 GPUs, 0.897 against 0.924 on 4, 0.9225 against 0.930 ms for the down-projection on 2
-            # (kept on push there)
-            pushable = partial == "f32" and m % (256 * world) == 0
-            mode = ("inkernel" if (pushable and world >= 4 and down_n % (128 * self.sub_blocks) == 0) else "push") if pushable else "fused"
+            mode = pick_exchange(world, partial, m, down_n, self.sub_blocks)
         self.overlap = mode == "overlap"
         self.push = mode == "push"
         self.pipelined = mode == "pipelined"

@@ -104,3 +104,14 @@ def test_balanced_decode_partition_arithmetic():
         for cb in range(cbs):
             first, last = cta_of(cb * ku, U, G), cta_of(cb * ku + ku - 1, U, G)
             assert sorted(set(owner[cb * ku:(cb + 1) * ku])) == list(range(first, last + 1))
+
+
+def test_automatic_exchange_choice():
+    """dist.pick_exchange: the form `--exchange auto` stands for, from the shapes alone."""
+    from awesome_fusion_b200 import dist
+    assert dist.pick_exchange(8, "f32", 4096, 8192) == "inkernel"
+    assert dist.pick_exchange(4, "f32", 4096, 8192) == "inkernel"
+    assert dist.pick_exchange(2, "f32", 4096, 8192) == "push"            # measured level on 2 GPUs: the simpler form stays
+    assert dist.pick_exchange(4, "f32", 4096, 8192 + 128) == "push"      # N is not a whole number of column chunks
+    assert dist.pick_exchange(4, "f32", 4096 + 256, 8192) == "fused"     # rows do not split into whole tiles per owner
+    assert dist.pick_exchange(8, "bf16", 4096, 8192) == "fused"          # bf16 partial sums travel only in the pull form
