@@ -271,37 +271,55 @@ SINGLE_CASES = {
 # ----------------------------------------------------------------------------------------
 # CPU arm: the reference's own gemm_rrr (host_ref.hpp) compiled into oracle/_ref, else the oracle port
 # ----------------------------------------------------------------------------------------
+class CpuArm:
+    """The reference's CPU GEMM (oracle/_ref when it was built from the reference's own headers, else the oracle port) on a bounded
+    sample of the headline workload: `rows` rows of C of the up-projection (N=28672, K=8192, all of N and K), one row-range per
+    host thread.  The weights are made once; the first run calibrates how many rows fit the time a step may take."""
+
+    def __init__(self):
+        import numpy as np
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import afb_testlib as T
+        self.np, self.T = np, T
+        self.cores = os.cpu_count() or 1
+        self.n, self.k = 28672, 8192
+        self.rng = np.random.default_rng(0)
+        self.ref = T.load_hostref()
+        self.kind = "reference" if self.ref is not None else "port"
+        # first guess: about 0.1 GFLOP/s per thread for the reference loop (B is read with stride N), 1.5 for the port
+        self.per_thread_gflops = 0.1 if self.ref is not None else 1.5
+        if self.ref is not None:
+            self.b = self.rng.integers(-127, 128, size=(self.k, self.n), dtype=np.int8).astype(np.float32)
+            self.s = self.rng.uniform(0.001, 0.01, self.n).astype(np.float32)
+        else:
+            self.orc = T.load_oracle()
+
+    def run(self, seconds_target):
+        """One sample of about seconds_target seconds.  Returns (tflops, info, seconds)."""
+        np, n, k = self.np, self.n, self.k
+        rows_per_thread = max(1, int(seconds_target * self.per_thread_gflops * 1e9 / (2.0 * n * k)))
+        rows = rows_per_thread * self.cores
+        if self.ref is not None:
+            a = self.rng.standard_normal((rows, k), dtype=np.float32)
+            fn = lambda: self.ref.gemm_rrr(a, self.b, self.s, threads=self.cores)
+        else:
+            case = self.T.make_case(rows, n, k, seed=0)
+            fn = lambda: self.orc.gemm(case, threads=self.cores)
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        self.per_thread_gflops = 2.0 * rows_per_thread * n * k / dt / 1e9   # the measured rate sizes the next sample
+        info = {"kind": self.kind, "cores": self.cores, "seconds": round(dt, 2),
+                "sample": f"{rows} of 4096 rows of C of the up-projection (M x 28672 x 8192, int8 per-channel), all N and K, "
+                          f"{rows_per_thread} row(s) per host thread; the down-projection has the same FLOPs"}
+        return 2.0 * rows * n * k / dt / 1e12, info, dt
+
+
 def cpu_arm(seconds_target=12.0):
-    """Times the reference's CPU GEMM on a bounded sample of the headline workload: `rows` rows of C of the
-    up-projection (N=28672, K=8192, all of N and K), one row-range per host thread.  Returns (tflops, info)."""
-    import numpy as np
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import afb_testlib as T
-    cores = os.cpu_count() or 1
-    n, k = 28672, 8192
-    rng = np.random.default_rng(0)
-    ref = T.load_hostref()
-    kind = "reference" if ref is not None else "port"
-    # about 0.2 GFLOP/s per thread for the reference loop (B is read with stride N), 1.8 for the port
-    per_thread_gflops = 0.2 if ref is not None else 1.5
-    rows_per_thread = max(1, int(seconds_target * per_thread_gflops * 1e9 / (2.0 * n * k)))
-    rows = rows_per_thread * cores
-    a = rng.standard_normal((rows, k), dtype=np.float32)
-    if ref is not None:
-        b = rng.integers(-127, 128, size=(k, n), dtype=np.int8).astype(np.float32)
-        s = rng.uniform(0.001, 0.01, n).astype(np.float32)
-        run = lambda: ref.gemm_rrr(a, b, s, threads=cores)
-    else:
-        orc = T.load_oracle()
-        case = T.make_case(rows, n, k, seed=0)
-        run = lambda: orc.gemm(case, threads=cores)
-    t0 = time.perf_counter()
-    run()
-    dt = time.perf_counter() - t0
-    info = {"kind": kind, "cores": cores, "seconds": round(dt, 2),
-            "sample": f"{rows} of 4096 rows of C of the up-projection (M x 28672 x 8192, int8 per-channel), all N and K, "
-                      f"{rows_per_thread} row(s) per host thread; the down-projection has the same FLOPs"}
-    return 2.0 * rows * n * k / dt / 1e12, info, dt
+    """One bounded sample for the `cpu_baseline` object of the main line: a short calibration run, then the sample."""
+    arm = CpuArm()
+    arm.run(1.0)
+    return arm.run(seconds_target)
 
 
 def run_reference_arm(args):
@@ -309,14 +327,16 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     steps, warm = max(1, args.steps), max(0, args.warmup)
-    # each step is one bounded sample; keep the whole run within a few minutes
-    per = max(2.0, min(12.0, 150.0 / (steps + warm)))
+    # each step is one bounded sample; the whole run (warm-up included) is held to about two minutes of CPU work
+    per = max(1.0, min(12.0, 120.0 / (steps + warm)))
+    arm = CpuArm()
+    arm.run(1.0)   # calibration of the sample size on this host
     for _ in range(warm):
-        cpu_arm(per)
+        arm.run(per)
     vals, total = [], 0.0
     info = None
     for _ in range(steps):
-        v, info, dt = cpu_arm(per)
+        v, info, dt = arm.run(per)
         vals.append(v); total += dt
     v = sum(vals) / len(vals)
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
