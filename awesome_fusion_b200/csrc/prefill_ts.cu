@@ -615,6 +615,7 @@ prefill_ts_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_con
                 else if (atomicCAS(p.status, 0, AFB_ERR_TIMEOUT) == 0) { p.status[1] = 16; p.status[2] = (int)c; p.status[3] = (int)p.x.epoch; }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();   // the other lanes' loads below are ordered after lane 0's acquire
             if (!ok) { failed = true; break; }
             for (uint32_t i = gw * 32u + (uint32_t)lane; i < total; i += nw * 32u) {
                 const uint32_t lr = i / vec_per_row, col = c * chunk_cols + (i - lr * vec_per_row) * 8u;
